@@ -7,7 +7,8 @@ layers, dynalm/src/kv_cache/kv_cache.cpp:31-38). Groups with different needs (al
 them, another entry shape) have pools and tables of their own. A group with a window gives pages
 back as soon as every token in them lies behind the window of the request's next token. Entries of
 kind "state" get one row per request slot in an array [slots, *state_shape], zeroed when a slot is
-handed out; every request takes a slot whether or not the model has such entries.
+handed out; every request takes a slot whether or not the model has such entries. An entry of
+kind "pages" whose spec gives a `state_shape` keeps such a row beside its pages.
 
 What is given back when: all pages and the slot when a request is freed (finished, cancelled,
 failed, or preempted for recompute: dynalm/src/runtime/sequence.cpp:44-63); windowed pages after
@@ -136,6 +137,12 @@ class CacheManager:
                     self.groups.append(g)
                 g.members.append(entry)
                 self.entry_group[entry] = g
+                if spec.state_shape:                      # pages that carry a state row
+                    self.state_specs[entry] = spec
+                    if self.device is not None:
+                        self.state_arrays[entry] = torch.zeros((self.max_requests,) + tuple(spec.state_shape),
+                                                               dtype=_torch_dtype(spec.state_dtype, torch.float32),
+                                                               device=self.device)
             elif spec.kind == "state":
                 self.state_specs[entry] = spec
                 if self.device is not None:
@@ -355,7 +362,8 @@ class CacheManager:
     def view(self, entry: int, block_tables: Dict[int, torch.Tensor]) -> Optional[CacheView]:
         g = self.entry_group.get(entry)
         if g is not None:
-            return CacheView("pages", g.arrays[entry], self.page_size, block_tables[g.gid])
+            state = CacheView("state", [self.state_arrays[entry]]) if entry in self.state_arrays else None
+            return CacheView("pages", g.arrays[entry], self.page_size, block_tables[g.gid], state)
         if entry in self.state_arrays:
             return CacheView("state", [self.state_arrays[entry]])
         return None

@@ -183,13 +183,16 @@ class EmbeddingSpec:
 @dataclass(frozen=True)
 class HeadSpec:
     """Final projection to the vocabulary. `tied` uses the embedding table; logits are
-    divided by `logit_divisor` (dynalm/src/model/transformer.cpp:719)."""
+    divided by `logit_divisor` (dynalm/src/model/transformer.cpp:719) and multiplied by `logit_scale`; with
+    `softcap` = c > 0 they then become c * tanh(logits / c)."""
 
     vocab: int
     width: int
     tied: bool
     logit_divisor: float = 1.0
     tensors: Dict[str, str] = field(default_factory=dict, hash=False, compare=False)
+    logit_scale: float = 1.0
+    softcap: float = 0.0
 
 
 @dataclass

@@ -23,7 +23,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
                                int max_blocks, const int* __restrict__ positions,
                                const int* __restrict__ row_request, T* __restrict__ out, int out_stride,
                                int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
-                               int window) {
+                               int window, int vdim, size_t k_row, size_t v_row) {
   __shared__ float red[33];
   __shared__ float sq[256];                 // the query, fp32
   __shared__ float sp[ATT_CHUNK];           // scores, then probabilities, of one chunk
@@ -40,9 +40,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
   __syncthreads();
 
   constexpr int V = PerVec<T>::n;
-  const int groups = ATT_THREADS / head_dim;          // >= 1 since head_dim <= 256
-  const int g = tid / head_dim, d = tid % head_dim;   // valid when g < groups
-  const size_t kv_row = static_cast<size_t>(n_kv_heads) * head_dim;
+  const int groups = ATT_THREADS / vdim;              // >= 1 since vdim <= 256
+  const int g = tid / vdim, d = tid % vdim;           // valid when g < groups
 
   float m_run = -INFINITY, l_run = 0.0f, acc = 0.0f;  // acc: dim `tid` of the output, threads < head_dim
   for (int c0 = (lo / ATT_CHUNK) * ATT_CHUNK; c0 <= pos; c0 += ATT_CHUNK) {
@@ -52,7 +51,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
       float s = -INFINITY;
       if (t >= lo) {
         const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
-        const Vec16* kr = reinterpret_cast<const Vec16*>(k_cache + slot * kv_row + static_cast<size_t>(kvh) * head_dim);
+        const Vec16* kr = reinterpret_cast<const Vec16*>(k_cache + slot * k_row + static_cast<size_t>(kvh) * head_dim);
         float dot = 0.0f;
         for (int i = 0; i < head_dim / V; ++i) {
           float f[V];
@@ -83,46 +82,62 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
       const int t0 = max(c0, lo);
       for (int t = t0 + g; t < c1; t += groups) {
         const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
-        pv = fmaf(sp[t - c0], to_float(v_cache[slot * kv_row + static_cast<size_t>(kvh) * head_dim + d]), pv);
+        pv = fmaf(sp[t - c0], to_float(v_cache[slot * v_row + static_cast<size_t>(kvh) * vdim + d]), pv);
       }
     }
     part[tid] = pv;
     __syncthreads();
-    if (tid < head_dim) {
+    if (tid < vdim) {
       float sum = 0.0f;
-      for (int gg = 0; gg < groups; ++gg) sum += part[gg * head_dim + tid];
+      for (int gg = 0; gg < groups; ++gg) sum += part[gg * vdim + tid];
       acc = acc * corr + sum;
     }
     __syncthreads();
   }
-  if (tid < head_dim) {
-    T* orow = out + static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * head_dim;
+  if (tid < vdim) {
+    T* orow = out + static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * vdim;
     orow[tid] = from_float<T>(acc / l_run);
   }
 }
 
 }  // namespace dl
 
-// q: rows of `q_stride` elements with head h at column h * head_dim; out likewise with out_stride.
-// k_cache, v_cache: [pages, page_size, n_kv_heads, head_dim]. head_dim: a multiple of 16 up to 256.
-DL_EXPORT int dl_paged_attention_generic(int dtype, const void* q, int q_stride, const void* k_cache,
-                                         const void* v_cache, const int* block_table, int max_blocks,
-                                         const int* positions, const int* row_request, void* out,
-                                         int out_stride, int rows, int n_heads, int n_kv_heads, int head_dim,
-                                         int page_size, float scale, int window, cudaStream_t stream) {
+// q: rows of `q_stride` elements with head h at column h * head_dim; out: rows of out_stride elements with head h at
+// column h * vdim. Keys of a token lie k_row elements apart from the next token's in k_cache (KV head j at j * head_dim),
+// values v_row elements apart in v_cache (KV head j at j * vdim): two arrays [pages, page_size, n_kv_heads, size], or
+// one array of records [k | v] given twice with two offsets. head_dim: a multiple of 16 up to 256 (bfloat16: every
+// key 16-byte aligned); vdim: 1 to 256.
+DL_EXPORT int dl_paged_attention_generic_kv(int dtype, const void* q, int q_stride, const void* k_cache, long long k_row,
+                                            const void* v_cache, long long v_row, const int* block_table, int max_blocks,
+                                            const int* positions, const int* row_request, void* out, int out_stride,
+                                            int rows, int n_heads, int n_kv_heads, int head_dim, int vdim, int page_size,
+                                            float scale, int window, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (head_dim % 16 != 0 || head_dim > 256 || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
-      page_size <= 0 || n_heads > 65535)
+  if (head_dim % 16 != 0 || head_dim > 256 || head_dim <= 0 || vdim <= 0 || vdim > 256 || n_kv_heads <= 0 ||
+      n_heads % n_kv_heads != 0 || page_size <= 0 || n_heads > 65535 || k_row % (dtype == 0 ? 4 : 8) != 0 ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 15) != 0)
     return DL_ERR_UNSUPPORTED;
   dim3 grid(rows, n_heads);
 #define DL_LAUNCH(T)                                                                                          \
   dl::paged_attention_generic_kernel<T><<<grid, dl::ATT_THREADS, 0, stream>>>(                                 \
       static_cast<const T*>(q), q_stride, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, positions, row_request, static_cast<T*>(out), out_stride, n_heads, n_kv_heads, \
-      head_dim, page_size, scale, window)
+      head_dim, page_size, scale, window, vdim, static_cast<size_t>(k_row), static_cast<size_t>(v_row))
   if (dtype == 0) DL_LAUNCH(float);
   else if (dtype == 1) DL_LAUNCH(dl::bf16);
   else return DL_ERR_UNSUPPORTED;
 #undef DL_LAUNCH
   return dl::launch_status();
+}
+
+// The same for keys and values of one size in two arrays [pages, page_size, n_kv_heads, head_dim].
+DL_EXPORT int dl_paged_attention_generic(int dtype, const void* q, int q_stride, const void* k_cache,
+                                         const void* v_cache, const int* block_table, int max_blocks,
+                                         const int* positions, const int* row_request, void* out,
+                                         int out_stride, int rows, int n_heads, int n_kv_heads, int head_dim,
+                                         int page_size, float scale, int window, cudaStream_t stream) {
+  const long long kv_row = static_cast<long long>(n_kv_heads) * head_dim;
+  return dl_paged_attention_generic_kv(dtype, q, q_stride, k_cache, kv_row, v_cache, kv_row, block_table, max_blocks,
+                                       positions, row_request, out, out_stride, rows, n_heads, n_kv_heads, head_dim,
+                                       head_dim, page_size, scale, window, stream);
 }

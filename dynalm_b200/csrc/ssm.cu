@@ -28,7 +28,7 @@ __global__ void ssm_conv_kernel(const T* __restrict__ proj, int proj_stride, int
                                 const float* __restrict__ state, size_t state_stride, size_t keep_off,
                                 const int* __restrict__ positions, const int* __restrict__ row_request,
                                 const int* __restrict__ row_slot, const int* __restrict__ pos_start,
-                                T* __restrict__ out, int rows) {
+                                T* __restrict__ out, int rows, int act, const float* __restrict__ in_bias) {
   const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<size_t>(rows) * channels) return;
   const int row = static_cast<int>(idx / channels), ch = static_cast<int>(idx % channels);
@@ -36,14 +36,16 @@ __global__ void ssm_conv_kernel(const T* __restrict__ proj, int proj_stride, int
   const int first = pos_start[ck_request(row_request[row])];      // the position of the request's first row in this step
   const float* kept = state + static_cast<size_t>(ck_request(row_slot[row])) * state_stride + keep_off;
   float acc = bias ? bias[ch] : 0.0f;
+  const float ib = in_bias ? in_bias[ch] : 0.0f;                   // joins every input that lies inside the sequence
   for (int k = K - 1; k >= 0; --k) {                               // oldest input first
     const int p = pos - k;
     float v;
     if (p >= first) v = to_float(proj[static_cast<size_t>(row - k) * proj_stride + col0 + ch]);
     else v = kept[static_cast<size_t>(K - 1 - (first - p)) * channels + ch];
+    if (p >= 0) v += ib;
     acc = fmaf(taps[static_cast<size_t>(K - 1 - k) * channels + ch], v, acc);
   }
-  out[idx] = from_float<T>(silu_f(acc));
+  out[idx] = from_float<T>(act ? silu_f(acc) : acc);
 }
 
 // The same with a thread on 8 (bfloat16) or 4 (float32) neighbouring channels of a row, 16 bytes a load: for channel
@@ -54,7 +56,7 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
                                     const float* __restrict__ state, size_t state_stride, size_t keep_off,
                                     const int* __restrict__ positions, const int* __restrict__ row_request,
                                     const int* __restrict__ row_slot, const int* __restrict__ pos_start,
-                                    T* __restrict__ out, int rows) {
+                                    T* __restrict__ out, int rows, int act, const float* __restrict__ in_bias) {
   constexpr int V = PerVec<T>::n;
   const int per_row = channels / V;
   const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -79,6 +81,10 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
 #pragma unroll
       for (int j = 0; j < V; ++j) v[j] = kr[j];          // (kept inputs begin where the state's layout puts them: no wide loads)
     }
+    if (in_bias != nullptr && p >= 0) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) v[j] += in_bias[ch + j];
+    }
     const float* tk = taps + static_cast<size_t>(K - 1 - k) * channels + ch;
 #pragma unroll
     for (int j = 0; j < V; j += 4) {
@@ -87,8 +93,10 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
       acc[j + 2] = fmaf(t4.z, v[j + 2], acc[j + 2]); acc[j + 3] = fmaf(t4.w, v[j + 3], acc[j + 3]);
     }
   }
+  if (act) {
 #pragma unroll
-  for (int j = 0; j < V; ++j) acc[j] = silu_f(acc[j]);
+    for (int j = 0; j < V; ++j) acc[j] = silu_f(acc[j]);
+  }
   *reinterpret_cast<Vec16*>(out + static_cast<size_t>(row) * channels + ch) = pack<T>(acc);
 }
 
@@ -389,10 +397,13 @@ __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T
 // out[row, ch] = silu(bias[ch] + sum_k taps[k, ch] * input(row's position - (K - 1 - k), ch)), the inputs being
 // columns col0 .. col0 + channels of proj; taps: float32 [K, channels], tap by tap (the model file's [channels, K]
 // transposed, so that neighbouring channels read neighbouring words). state: [slots, state_stride] float32, a slot's kept inputs at keep_off.
-DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0, int channels, const float* taps,
-                          const float* bias, int K, const float* state, long long state_stride, long long keep_off,
-                          const int* positions, const int* row_request, const int* row_slot, const int* pos_start,
-                          void* out, int rows, cudaStream_t stream) {
+// The convolution with its options: act 1 = silu on the result, 0 = none; in_bias (float32 [channels], may be null) is
+// added to every input that lies inside the sequence before the taps (the bias of the projection that made the
+// inputs, where that product runs without it); kept inputs are stored without it.
+DL_EXPORT int dl_short_conv(int dtype, const void* proj, int proj_stride, int col0, int channels, const float* taps,
+                            const float* bias, int K, const float* state, long long state_stride, long long keep_off,
+                            const int* positions, const int* row_request, const int* row_slot, const int* pos_start,
+                            void* out, int rows, int act, const float* in_bias, cudaStream_t stream) {
   if (rows <= 0 || channels <= 0) return 0;
   if (K <= 0) return DL_ERR_UNSUPPORTED;
   const int threads = 256;
@@ -406,13 +417,22 @@ DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0
 #define DL_LAUNCH(KERNEL, T)                                                                                         \
   dl::KERNEL<T><<<blocks, threads, 0, stream>>>(static_cast<const T*>(proj), proj_stride, col0, channels, taps, bias, K, \
                                                 state, static_cast<size_t>(state_stride), static_cast<size_t>(keep_off), \
-                                                positions, row_request, row_slot, pos_start, static_cast<T*>(out), rows)
+                                                positions, row_request, row_slot, pos_start, static_cast<T*>(out), rows, \
+                                                act, in_bias)
   if (dtype == 0 && wide) DL_LAUNCH(ssm_conv_vec_kernel, float);
   else if (dtype == 0) DL_LAUNCH(ssm_conv_kernel, float);
   else if (wide) DL_LAUNCH(ssm_conv_vec_kernel, dl::bf16);
   else DL_LAUNCH(ssm_conv_kernel, dl::bf16);
 #undef DL_LAUNCH
   return dl::launch_status();
+}
+
+DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0, int channels, const float* taps,
+                          const float* bias, int K, const float* state, long long state_stride, long long keep_off,
+                          const int* positions, const int* row_request, const int* row_slot, const int* pos_start,
+                          void* out, int rows, cudaStream_t stream) {
+  return dl_short_conv(dtype, proj, proj_stride, col0, channels, taps, bias, K, state, state_stride, keep_off, positions,
+                       row_request, row_slot, pos_start, out, rows, 1, nullptr, stream);
 }
 
 DL_EXPORT int dl_ssm_conv_keep(int dtype, const void* proj, int proj_stride, int col0, int channels, int K, float* state,

@@ -18,12 +18,14 @@ class CacheView:
     request has no page yet). The table lives on the device; a step sends only what changed.
     kind "state": `arrays[0]` is [slots, *state_shape]; the step's request r owns row
     `ctx.state_slots[r]`.
+    `state`: for an entry that keeps a state row beside its pages, the view of kind "state" of that row.
     """
 
     kind: str
     arrays: List[torch.Tensor]
     page_size: int = 0
     block_table: Optional[torch.Tensor] = None
+    state: Optional["CacheView"] = None
 
 
 @dataclass

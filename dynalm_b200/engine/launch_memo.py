@@ -125,6 +125,8 @@ class LayerLaunchMemo:
             tensors = owned_tensors(block)
             if cache is not None:
                 tensors = tensors + list(cache.arrays) + ([cache.block_table] if cache.block_table is not None else [])
+                if cache.state is not None:
+                    tensors = tensors + list(cache.state.arrays)
             got = (cache, _Layout(tensors))
             self.layouts[index] = got
         return got[1]

@@ -37,7 +37,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to a page)")
     ap.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default: the engine's)")
-    ap.add_argument("--max-requests", type=int, default=8, help="most requests alive at once")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests alive at once (state slots)")
     ap.add_argument("--summary", default=None, help="also write a text line per wanted place to this file")
     args = ap.parse_args(argv)
 

@@ -174,6 +174,16 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
     return act
 
 
+def linear_geglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int) -> torch.Tensor:
+    """gelu_tanh(x Wg^T) * (x Wu^T) with w_gate_up = [Wg; Wu]: the product followed by the activation kernel."""
+    rows = x.shape[0]
+    act = runtime.buffer("ffn_act", (rows, inner))
+    gate_up = runtime.buffer("ffn_gate_up", (rows, 2 * inner))
+    linear(x, w_gate_up, gate_up)
+    ops.gelu_mul(gate_up, act)
+    return act
+
+
 def linear_act(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int, activation: str) -> torch.Tensor:
     """act(x W^T), the first half of an ungated feed-forward, act = "relu2" (max(z, 0)^2) or "gelu_tanh": the
     activation sits in the product's epilogue wherever one of this package's bfloat16 kernels runs the product, else

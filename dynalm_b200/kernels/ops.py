@@ -35,6 +35,7 @@ _SIGNATURES = {
         "dl_cast_rows": [_I, _P, _P, _L, _P]},
     "ssm": {
         "dl_ssm_conv": [_I, _P, _I, _I, _I, _P, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _I, _P],
+        "dl_short_conv": [_I, _P, _I, _I, _I, _P, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _I, _I, _P, _P],
         "dl_ssm_conv_keep": [_I, _P, _I, _I, _I, _I, _P, _L, _L, _P, _P, _I, _P],
         "dl_ssm_scan": [_I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P,
                         _P, _P],
@@ -64,7 +65,25 @@ _SIGNATURES = {
         "dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P],
         "dl_rope_angles": [_P, _P, _I, _F, _I, _P, _P]},
     "attention_generic": {
-        "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
+        "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "dl_paged_attention_generic_kv": [_I, _P, _I, _P, _L, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
+                                          _P]},
+    "delta_rule": {
+        "dl_delta_rule": [_I, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "dl_head_norm_gate": [_I, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _P]},
+    "rglru": {
+        "dl_rglru_gates": [_I, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
+        "dl_rglru_scan": [_I, _P, _P, _P, _I, _I, _P, _P, _L, _P, _P, _P, _I, _I, _P]},
+    "qk_proj_norm": {
+        "dl_qk_proj_norm_cache": [_I, _P, _I, _P, _P, _F, _I, _P, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I,
+                                  _I, _I, _P]},
+    "gates": {
+        "dl_gelu_mul": [_I, _P, _P, _I, _I, _P],
+        "dl_sigmoid_gate": [_I, _P, _I, _P, _I, _I, _I, _P],
+        "dl_scaled_sum": [_I, _P, _I, _L, _F, _I, _P, _I, _L, _F, _P, _L, _P],
+        "dl_softcap": [_P, _L, _F, _P]},
+    "norm_sandwich": {
+        "dl_norm_add_norm": [_I, _I, _P, _P, _I, _L, _P, _F, _P, _F, _P, _I, _I, _P]},
     "attention_decode": {
         "dl_paged_attention_decode": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "dl_paged_attention_decode_planned": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P,
@@ -1593,3 +1612,228 @@ def sample_filtered(logits: torch.Tensor, rows: torch.Tensor, n_sel: int, dparam
         check_limits("sampling", rows=min(logits.shape[0], out.numel()))      # a row is also a place in `out`
     _check(_fn("sampling", "dl_sample_filtered")(_p(logits), logits.stride(0), logits.shape[1], _p(rows), int(n_sel),
                                                   _p(dparams), _p(top_k), _p(out), _stream()), "sample_filtered")
+
+
+# ---------------------------------------------------------------------------------------------
+# short convolutions with options, the gated delta rule, the gated linear recurrence, whole-projection query/key norms,
+# gates and caps
+
+def _state_rows(state: torch.Tensor, need: int, what: str) -> None:
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < need:
+        raise InvalidArgument(f"{what}: state float32 [slots, >= {need}]")
+
+
+def short_conv(proj: torch.Tensor, col0: int, channels: int, taps_t: torch.Tensor, bias: Optional[torch.Tensor],
+               state: torch.Tensor, keep_off: int, positions: torch.Tensor, row_request: torch.Tensor,
+               row_slot: torch.Tensor, pos_start: torch.Tensor, out: torch.Tensor, act: str = "silu",
+               in_bias: Optional[torch.Tensor] = None) -> None:
+    """ssm_conv with its options: act "silu" or "none" on the result; in_bias (float32 [channels]) joins every input
+    that lies inside the sequence before the taps (kept inputs are stored without it). See csrc/ssm.cu."""
+    taps = taps_t
+    _cuda(proj, taps, bias, state, positions, row_request, row_slot, pos_start, out, in_bias)
+    _rows_contiguous(proj, "proj")
+    rows, K = proj.shape[0], taps.shape[0]
+    if act not in ("silu", "none"):
+        raise InvalidArgument(f"short_conv: no activation '{act}' (silu, none)")
+    if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.dim() != 2 or taps.shape[1] != channels:
+        raise InvalidArgument("short_conv: taps float32 [K, channels]")
+    for b in (bias, in_bias):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != channels):
+            raise InvalidArgument("short_conv: a bias is float32 [channels]")
+    _state_rows(state, keep_off + (K - 1) * channels, "short_conv")
+    if out.dtype != proj.dtype or out.shape != (rows, channels) or not out.is_contiguous() or col0 + channels > proj.shape[1]:
+        raise InvalidArgument("short_conv: out contiguous [rows, channels] of proj's dtype; the channels lie inside proj")
+    check_limits("ssm", requests=state.shape[0], rows=rows)
+    _check(_fn("ssm", "dl_short_conv")(dtype_code(proj.dtype), _p(proj), proj.stride(0), col0, channels, _p(taps), _p(bias), K,
+                                        _p(state), state.stride(0), keep_off, _p(positions), _p(row_request), _p(row_slot),
+                                        _p(pos_start), _p(out), rows, 1 if act == "silu" else 0, _p(in_bias), _stream()),
+           "short_conv")
+
+
+def delta_rule(u: torch.Tensor, q_col: int, k_col: int, v_col: int, proj: torch.Tensor, b_col: int, a_col: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+               state_slots: torch.Tensor, out: torch.Tensor, requests: int, heads: int, kv_heads: int, dim: int,
+               vdim: int) -> None:
+    """The gated delta rule of every head over every request's rows of the step, from and into state[slot, :H*d*e]
+    ([H, d, e]). u: rows with q (G*d) at q_col, k (G*d) at k_col, v (H*e) at v_col, after convolution and silu; proj:
+    rows with the raw write strengths (H) at b_col and the raw step sizes (H) at a_col; out: float32 [rows, H*e].
+    See csrc/delta_rule.cu."""
+    _cuda(u, proj, a_log, dt_bias, state, q_start, state_slots, out)
+    _rows_contiguous(u, "u")
+    _rows_contiguous(proj, "proj")
+    if u.dtype != proj.dtype or max(q_col, k_col) + kv_heads * dim > u.shape[1] or v_col + heads * vdim > u.shape[1] \
+            or max(b_col, a_col) + heads > proj.shape[1]:
+        raise InvalidArgument("delta_rule: the columns lie outside u or proj, or their dtypes differ")
+    if any(t.dtype != torch.float32 or t.numel() != heads for t in (a_log, dt_bias)):
+        raise InvalidArgument("delta_rule: a_log and dt_bias are float32 [heads]")
+    if heads % kv_heads or dim > 512:
+        raise Unsupported(f"delta_rule: {heads} heads over {kv_heads} query/key heads of {dim} (at most 512) has no kernel")
+    _state_rows(state, heads * dim * vdim, "delta_rule")
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (u.shape[0], heads * vdim):
+        raise InvalidArgument("delta_rule: out float32 contiguous [rows, H*e]")
+    check_limits("delta_rule", requests=state.shape[0], rows=u.shape[0])
+    _check(_fn("delta_rule", "dl_delta_rule")(dtype_code(u.dtype), _p(u), u.stride(0), q_col, k_col, v_col, _p(proj),
+                                               proj.stride(0), b_col, a_col, _p(a_log), _p(dt_bias), _p(state),
+                                               state.stride(0), _p(q_start), _p(state_slots), _p(out), requests, heads,
+                                               kv_heads, dim, vdim, _stream()), "delta_rule")
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                   heads: int, vdim: int) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, gate_col + h * e ...]).
+    o: float32 contiguous [rows, H*e]; weight: float32 [e]; out: contiguous [rows, H*e] of gate's dtype."""
+    _cuda(o, gate, weight, out)
+    _rows_contiguous(gate, "gate")
+    rows = o.shape[0]
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape != (rows, heads * vdim) or weight.dtype != torch.float32 \
+            or weight.numel() != vdim or out.shape != o.shape or not out.is_contiguous() or out.dtype != gate.dtype \
+            or gate_col + heads * vdim > gate.shape[1] or gate.shape[0] < rows:
+        raise InvalidArgument("head_norm_gate: o float32 [rows, H*e], weight float32 [e], out [rows, H*e] of the gate's dtype")
+    _check(_fn("delta_rule", "dl_head_norm_gate")(dtype_code(gate.dtype), _p(o), _p(gate), gate.stride(0), gate_col,
+                                                   _p(weight), eps, _p(out), rows, heads, vdim, _stream()), "head_norm_gate")
+
+
+def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, ba: torch.Tensor, wi_t: torch.Tensor, bi: torch.Tensor,
+                lam: torch.Tensor, decay_scale: float, a_out: torch.Tensor, m_out: torch.Tensor) -> None:
+    """Per row and channel the decay a and the gated input m of a real-gated linear recurrent unit. u: contiguous [rows,
+    width]; wa_t, wi_t: float32 [blocks, in, out]; ba, bi, lam: float32 [width]; a_out, m_out: float32 [rows, width].
+    See csrc/rglru.cu."""
+    _cuda(u, wa_t, ba, wi_t, bi, lam, a_out, m_out)
+    rows, width = u.shape
+    blocks = wa_t.shape[0]
+    nb = width // max(blocks, 1)
+    if not u.is_contiguous() or any(t.dtype != torch.float32 or not t.is_contiguous() for t in (wa_t, ba, wi_t, bi, lam, a_out, m_out)) \
+            or tuple(wa_t.shape) != (blocks, nb, nb) or wi_t.shape != wa_t.shape or blocks * nb != width \
+            or any(t.numel() != width for t in (ba, bi, lam)) or a_out.shape != u.shape or m_out.shape != u.shape:
+        raise InvalidArgument("rglru_gates: shapes or dtypes disagree")
+    _check(_fn("rglru", "dl_rglru_gates")(dtype_code(u.dtype), _p(u), _p(wa_t), _p(ba), _p(wi_t), _p(bi), _p(lam),
+                                           decay_scale, _p(a_out), _p(m_out), rows, width, blocks, _stream()), "rglru_gates")
+
+
+def rglru_scan(a: torch.Tensor, m: torch.Tensor, y: torch.Tensor, y_col: int, y_bias: Optional[torch.Tensor],
+               state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
+               requests: int) -> None:
+    """S <- a S + m along every request's rows of the step, from and into state[slot, :width]; out = S *
+    gelu_tanh(y[:, y_col ...] + y_bias). a, m: float32 [rows, width]; out: contiguous [rows, width] of y's dtype."""
+    _cuda(a, m, y, y_bias, state, q_start, state_slots, out)
+    _rows_contiguous(y, "y")
+    rows, width = a.shape
+    if a.dtype != torch.float32 or m.dtype != torch.float32 or not a.is_contiguous() or not m.is_contiguous() \
+            or m.shape != a.shape or out.shape != a.shape or not out.is_contiguous() or out.dtype != y.dtype \
+            or y_col + width > y.shape[1] or (y_bias is not None and (y_bias.dtype != torch.float32 or y_bias.numel() != width)):
+        raise InvalidArgument("rglru_scan: shapes or dtypes disagree")
+    _state_rows(state, width, "rglru_scan")
+    check_limits("rglru", requests=state.shape[0], rows=rows)
+    _check(_fn("rglru", "dl_rglru_scan")(dtype_code(y.dtype), _p(a), _p(m), _p(y), y.stride(0), y_col, _p(y_bias), _p(state),
+                                          state.stride(0), _p(q_start), _p(state_slots), _p(out), requests, width,
+                                          _stream()), "rglru_scan")
+
+
+def qk_proj_norm_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float, do_norm: bool,
+                       inv_freq: Optional[torch.Tensor], rot: int, pos_scale: float, positions: torch.Tensor,
+                       row_slot: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, k_row: int,
+                       v_cache: torch.Tensor, v_row: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                       page_size: int) -> None:
+    """Rows [q: H*d | k: G*d | v: G*e | ...] of a projection: q and k normed over the whole projection (one statistic
+    each, weights wq / wk), their heads' first `rot` numbers turned by position (pairs i, i + rot/2), q written back
+    in place, k and v written to the token's place in the cache: k_cache / v_cache point at the first token's keys /
+    values, k_row / v_row elements lie between two tokens. See csrc/qk_proj_norm.cu."""
+    _cuda(proj, wq, wk, inv_freq, positions, row_slot, block_table, k_cache, v_cache)
+    _rows_contiguous(proj, "proj")
+    if proj.shape[1] < heads * dim + kv_heads * (dim + vdim) or k_cache.dtype != proj.dtype or v_cache.dtype != proj.dtype:
+        raise InvalidArgument("qk_proj_norm_cache: proj holds q | k | v; the cache has proj's dtype")
+    for w, n in ((wq, heads * dim), (wk, kv_heads * dim)):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != n):
+            raise InvalidArgument("qk_proj_norm_cache: a norm weight is float32 over the whole projection")
+    if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
+        raise InvalidArgument("qk_proj_norm_cache: inv_freq float32 [rot / 2]")
+    check_limits("qk_proj_norm", pages=k_cache.shape[0], requests=block_table.shape[0], rows=proj.shape[0])
+    _check(_fn("qk_proj_norm", "dl_qk_proj_norm_cache")(
+        dtype_code(proj.dtype), _p(proj), proj.stride(0), _p(wq), _p(wk), eps, 1 if do_norm else 0, _p(inv_freq), rot,
+        pos_scale, _p(positions), _p(row_slot), _p(block_table), block_table.stride(0), _p(k_cache), k_row, _p(v_cache),
+        v_row, proj.shape[0], heads, kv_heads, dim, vdim, page_size, _stream()), "qk_proj_norm_cache")
+
+
+def paged_attention_generic_kv(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int,
+                               block_table: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,
+                               out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, vdim: int, page_size: int,
+                               scale: float, window: int = 0) -> None:
+    """paged_attention_generic with keys of head_dim and values of vdim numbers: k_cache / v_cache point at the first
+    token's keys / values (KV head j at j * head_dim / j * vdim), k_row / v_row elements lie between two tokens.
+    out: rows with head h at column h * vdim."""
+    _cuda(q, k_cache, v_cache, block_table, positions, row_request, out)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if head_dim % 16 or head_dim > 256 or not 0 < vdim <= 256:
+        raise Unsupported(f"attention: keys of {head_dim} (a multiple of 16, at most 256) and values of {vdim} (at most 256)")
+    if n_heads % n_kv_heads:
+        raise Unsupported(f"attention: {n_heads} heads do not divide into {n_kv_heads} KV heads")
+    if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise InvalidArgument("attention: q, out and the cache must share one dtype")
+    check_limits("attention_generic", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
+    _check(_fn("attention_generic", "dl_paged_attention_generic_kv")(
+        dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table),
+        block_table.stride(0), _p(positions), _p(row_request), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads,
+        head_dim, vdim, page_size, scale, window, _stream()), "paged_attention_generic_kv")
+
+
+def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(gate_up[t, j]) * gate_up[t, inner + j]."""
+    _cuda(gate_up, out)
+    rows, inner = out.shape
+    if gate_up.shape != (rows, 2 * inner) or gate_up.dtype != out.dtype or not gate_up.is_contiguous() or not out.is_contiguous():
+        raise InvalidArgument("gelu_mul: gate_up contiguous [rows, 2 * inner], out contiguous [rows, inner], one dtype")
+    _check(_fn("gates", "dl_gelu_mul")(dtype_code(out.dtype), _p(gate_up), _p(out), rows, inner, _stream()), "gelu_mul")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[t, j] <- x[t, j] * sigmoid(gate[t, j]) over x's columns; both 2-D views with unit column stride."""
+    _cuda(x, gate)
+    _rows_contiguous(x, "x")
+    _rows_contiguous(gate, "gate")
+    if x.dtype != gate.dtype or gate.shape[0] < x.shape[0] or gate.shape[1] < x.shape[1]:
+        raise InvalidArgument("sigmoid_gate: x and gate of one dtype, the gate at least as large as x")
+    _check(_fn("gates", "dl_sigmoid_gate")(dtype_code(x.dtype), _p(x), x.stride(0), _p(gate), gate.stride(0), x.shape[0],
+                                            x.shape[1], _stream()), "sigmoid_gate")
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b (float32 [n, width]); a and b are [n, width] or split-K partial sums [parts, n, width] of
+    either dtype, added in order."""
+    _cuda(a, b, out)
+    width = out.shape[-1]
+    pa, stride_a = _delta_parts(a, width, "scaled_sum")
+    pb, stride_b = _delta_parts(b, width, "scaled_sum")
+    if out.dtype != torch.float32 or not out.is_contiguous() or a.shape[-2:] != out.shape or b.shape[-2:] != out.shape:
+        raise InvalidArgument("scaled_sum: out float32 contiguous, of the shape of a and b")
+    _check(_fn("gates", "dl_scaled_sum")(dtype_code(a.dtype), _p(a), pa, stride_a, sa, dtype_code(b.dtype), _p(b), pb,
+                                          stride_b, sb, _p(out), out.numel(), _stream()), "scaled_sum")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; x float32 contiguous."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise InvalidArgument("softcap: x float32 contiguous")
+    _check(_fn("gates", "dl_softcap")(_p(x), x.numel(), cap, _stream()), "softcap")
+
+
+def norm_add_norm(x: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, eps_post: float,
+                  w_pre: Optional[torch.Tensor] = None, eps_pre: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+    """x <- x + rmsnorm(delta) * w_post, then (with w_pre) out = rmsnorm(x) * w_pre. x: float32 [n, width] in place;
+    delta: [n, width] of either dtype or partial sums [parts, n, width]; out: [n, width]. See csrc/norm_sandwich.cu."""
+    _cuda(x, delta, w_post, w_pre, out)
+    rows, width = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or w_post.dtype != torch.float32 or w_post.numel() != width:
+        raise InvalidArgument("norm_add_norm: x float32 contiguous, w_post float32 [width]")
+    if (w_pre is None) != (out is None) or (w_pre is not None and (w_pre.dtype != torch.float32 or w_pre.numel() != width
+                                                                  or out.shape != x.shape or not out.is_contiguous())):
+        raise InvalidArgument("norm_add_norm: w_pre float32 [width] together with out contiguous [n, width], or neither")
+    parts, part_stride = _delta_parts(delta, width, "norm_add_norm")
+    if delta.shape[-2] < rows:
+        raise InvalidArgument("norm_add_norm: delta has fewer rows than x")
+    od = dtype_code(out.dtype) if out is not None else 0
+    _take_ahead()
+    _check(_fn("norm_sandwich", "dl_norm_add_norm")(od, dtype_code(delta.dtype), _p(x), _p(delta), parts, part_stride,
+                                                     _p(w_post), eps_post, _p(w_pre), eps_pre, _p(out), rows, width,
+                                                     _stream()), "norm_add_norm")

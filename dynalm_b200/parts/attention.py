@@ -152,3 +152,111 @@ class PagedAttention:
             return
         ops.paged_attention_generic(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_slot, out,
                                     s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, float(s.scale), s.get("window", 0))
+
+
+@register_mixer("gated_attention")
+class GatedNormedAttention(PagedAttention):
+    """Grouped-query attention with keys of head_dim and values of value_dim numbers, queries and keys normed over
+    their WHOLE projection before the heads are cut (one statistic for all H * d numbers of q, one for the G * d of k;
+    plain weights), a rotation of the first `rotary_dim` numbers of every head, a window, and an output gate: the
+    concatenated heads times sigmoid(W_g h) before the output projection. One product gives [q | k | v | gate].
+
+    Parameters: num_heads, num_kv_heads, head_dim, value_dim, scale, window, eps, qk_norm ("projection" or "none"),
+    gated (bool), position. Tensors: q, k, v, o, and by the parameters q_norm, k_norm, gate.
+
+    Where keys and values have one size the cache is the plain attention's (two arrays) and so are the kernels that
+    read it; otherwise a token's keys and values form one record [k | v] in one array, read by the plain kernel."""
+
+    out_name = "mixer_out"     # the workspace buffer of the result; a mixer that holds this one may name another
+
+    @staticmethod
+    def declare(spec) -> Dict[str, TensorDecl]:
+        qw, kw, vw = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.num_kv_heads * spec.value_dim
+        ow = spec.num_heads * spec.value_dim
+        normed, gated = spec.get("qk_norm", "none") == "projection", bool(spec.get("gated", False))
+        return {
+            "q": TensorDecl((qw, spec.width)), "k": TensorDecl((kw, spec.width)), "v": TensorDecl((vw, spec.width)),
+            "o": TensorDecl((spec.width, ow)),
+            "q_norm": TensorDecl((qw,), role="vector", required=normed, init="around_one"),
+            "k_norm": TensorDecl((kw,), role="vector", required=normed, init="around_one"),
+            "gate": TensorDecl((ow, spec.width), required=gated),
+        }
+
+    def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
+        if spec.head_dim % 16 or not 0 < spec.head_dim <= 256 or not 0 < spec.value_dim <= 256:
+            raise Unsupported(f"gated_attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256, and "
+                              f"value_dim {spec.value_dim} at most 256")
+        if spec.num_heads % spec.num_kv_heads:
+            raise Unsupported(f"gated_attention: {spec.num_heads} heads do not divide into {spec.num_kv_heads} KV heads")
+        if spec.get("qk_norm", "none") not in ("projection", "none"):
+            raise Unsupported(f"gated_attention: no query/key norm '{spec.qk_norm}' (projection, none)")
+        self.spec = spec
+        self.rt = runtime
+        self.q_width = spec.num_heads * spec.head_dim
+        self.kv_width = spec.num_kv_heads * spec.head_dim
+        self.v_width = spec.num_kv_heads * spec.value_dim
+        self.o_width = spec.num_heads * spec.value_dim
+        self.normed = spec.get("qk_norm", "none") == "projection"
+        self.gated = bool(spec.get("gated", False))
+        self.same = spec.head_dim == spec.value_dim          # keys and values of one size: the plain attention's cache
+        mats = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["gate"]] if self.gated else [])
+        self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        self.b_qkv = None
+        self.q_norm, self.k_norm = (tensors["q_norm"], tensors["k_norm"]) if self.normed else (None, None)
+        self.w_o = tensors["o"]
+        self.b_o = None
+        self.eps = float(spec.get("eps", 1e-6))
+        pos = spec.get("position")
+        self.position = POSITIONS.get(pos.kind)(pos, runtime) if pos is not None else None
+        if self.position is not None and self.position.table() is None:
+            raise Unsupported("gated_attention: the rotation runs inside its kernel and takes a position encoding with a table")
+
+    def step_plans(self) -> list:
+        return super().step_plans() if self.same else []
+
+    def graph_key(self, ctx) -> tuple:
+        return super().graph_key(ctx) if self.same and self.rt.dtype == torch.bfloat16 else ()
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        s = self.spec
+        if self.same:
+            return CacheSpec(kind="pages", entry_shape=(s.num_kv_heads, s.head_dim), tensors=2, window=s.get("window", 0))
+        return CacheSpec(kind="pages", entry_shape=(self.kv_width + self.v_width,), tensors=1, window=s.get("window", 0))
+
+    def _kv(self, cache):
+        """(keys of the first token, elements between tokens, values of the first token, elements between tokens)."""
+        if self.same:
+            k_cache, v_cache = cache.arrays
+            return k_cache, self.kv_width, v_cache, self.v_width
+        (records,) = cache.arrays
+        row = self.kv_width + self.v_width
+        return records, row, records.view(-1)[self.kv_width:], row
+
+    def forward(self, x: torch.Tensor, ctx, cache, owns_cache: bool = True) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        if not owns_cache:
+            raise Unsupported("gated_attention: every run of the layer keeps a cache of its own")
+        rows = x.shape[0]
+        proj = rt.buffer("gattn_proj", (rows, self.w_qkv.shape[0]))
+        linear(x, self.w_qkv, proj)
+        inv_freq, rot, pos_scale = self.position.table() if self.position is not None else (None, 0, 1.0)
+        k_cache, k_row, v_cache, v_row = self._kv(cache)
+        ops.qk_proj_norm_cache(proj, self.q_norm, self.k_norm, self.eps, self.normed, inv_freq, rot, pos_scale,
+                               ctx.positions, ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row,
+                               s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size)
+        attn = rt.buffer("gattn_out", (rows, self.o_width))
+        self.attend(proj, cache, ctx, attn)
+        if self.gated:
+            ops.sigmoid_gate(attn, proj[:, self.q_width + self.kv_width + self.v_width:])
+        return linear_partial(attn, self.w_o, rt, self.out_name)
+
+    def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
+        s = self.spec
+        if self.same:
+            from ..kernels import attention as fast
+            if fast.paged_attention(qkv, cache, ctx, out, s, self.rt):
+                return
+        k_cache, k_row, v_cache, v_row = self._kv(cache)
+        ops.paged_attention_generic_kv(qkv, k_cache, k_row, v_cache, v_row, cache.block_table, ctx.positions, ctx.row_slot,
+                                       out, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
+                                       float(s.scale), s.get("window", 0))

@@ -51,6 +51,8 @@ class CacheSpec:
     are ever read, so pages wholly behind the window are given back.
     kind "state": one array [slots, *state_shape] indexed by the request's state slot,
     zeroed when a slot is handed out.
+    A spec of kind "pages" may give a `state_shape` too: the entry then keeps such a state row beside its pages (a
+    mixer that runs attention and a recurrence side by side), of `state_dtype`.
     """
 
     kind: str
@@ -59,9 +61,10 @@ class CacheSpec:
     window: int = 0
     state_shape: Tuple[int, ...] = ()
     dtype: Optional[str] = None      # None = the compute dtype; else "float32" / "bfloat16"
+    state_dtype: Optional[str] = None      # of the state row beside pages; None = float32
 
     def group_key(self) -> tuple:
-        return (self.kind, self.entry_shape, self.tensors, self.window, self.state_shape, self.dtype)
+        return (self.kind, self.entry_shape, self.tensors, self.window, self.state_shape, self.dtype, self.state_dtype)
 
 
 class _Registry:

@@ -169,3 +169,36 @@ class PostNormBlock(Block):
             self.ffn_norm.forward(stream.x, h if narrow else None, f)
         stream.as_input = h if narrow else None
         return stream
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Block):
+    """parts: mixer_norm, mixer, mixer_post_norm, and optionally ffn_norm, ffn, ffn_post_norm: a norm in front of
+    every sublayer and one behind it, before its result joins the stream: x <- x + post1(mixer(pre1(x))), then x <- x +
+    post2(ffn(pre2(x))). The norm behind the mixer, the sum and the norm in front of the feed-forward are one kernel
+    (ops.norm_add_norm), which keeps the row in shared memory between the two; the stream is float32 and nothing is
+    left pending."""
+
+    def __init__(self, spec, store, runtime):
+        super().__init__(spec, store, runtime)
+        self.has_ffn = "ffn" in spec.parts
+
+    def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
+        rows, width = stream.x.shape
+        stream.flush_second()                      # (an arrangement that leaves its outputs pending may stand in front)
+        h = self.rt.buffer("normed", (rows, width))
+        self.mixer_norm.forward(stream.x, h, delta=stream.pending, delta_scale=stream.pending_scale)
+        stream.pending = None
+        a = self.mixer.forward(h, ctx, cache, owns_cache)
+        post = self.mixer_post_norm
+        if self.has_ffn:
+            h = self.rt.buffer("normed", (rows, width))
+            ops.norm_add_norm(stream.x, a, post.weight, post.eps, self.ffn_norm.weight, self.ffn_norm.eps, h)
+            f = self.ffn.forward(h, ctx)
+            post = self.ffn_post_norm
+            ops.norm_add_norm(stream.x, f, post.weight, post.eps)
+        else:
+            ops.norm_add_norm(stream.x, a, post.weight, post.eps)
+        stream.pending_scale = 1.0
+        stream.as_input = None
+        return stream

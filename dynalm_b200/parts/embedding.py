@@ -35,17 +35,23 @@ class TokenEmbedding:
 
 
 class LogitsHead:
-    """logits = normed rows x head^T / divisor, float32 [rows, vocab]
-    (dynalm/src/model/transformer.cpp:703-719). `tied` uses the embedding table."""
+    """logits = normed rows x head^T / divisor * scale, float32 [rows, vocab]
+    (dynalm/src/model/transformer.cpp:703-719), then capped by c * tanh(logits / c) when the spec gives a cap (which
+    keeps their order, so the most likely token may still be chosen inside the product). `tied` uses the embedding
+    table."""
 
     def __init__(self, spec, store, runtime, embedding: TokenEmbedding):
         self.spec = spec
         self.rt = runtime
         self.weight = embedding.table if spec.tied else store[spec.tensors["weight"]]
         self.out_scale = 1.0 / float(spec.logit_divisor) if spec.logit_divisor != 1.0 else 1.0
+        self.out_scale *= float(getattr(spec, "logit_scale", 1.0))
+        self.softcap = float(getattr(spec, "softcap", 0.0))
 
     def forward(self, normed_rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         linear(normed_rows, self.weight, out, None, self.out_scale)
+        if self.softcap > 0.0:
+            ops.softcap(out, self.softcap)         # c * tanh(logits / c), in place on the float32 logits
         return out
 
     def choose(self, normed_rows: torch.Tensor, ids: torch.Tensor, status_to=None) -> bool:

@@ -1,5 +1,6 @@
 """Gated feed-forward: down(act(gate x) * up x), the "gated_mlp" kind
-(dynalm/src/model/transformer.cpp:671-693). Gate and up run as one product against [Wg; Wu].
+(dynalm/src/model/transformer.cpp:671-693), act silu or the tanh form of GELU (parameter `activation`). Gate and up
+run as one product against [Wg; Wu].
 Ungated feed-forward: down(act(up x)), the "mlp" kind, act the squared ReLU or the tanh form of GELU."""
 
 from __future__ import annotations
@@ -10,7 +11,7 @@ import torch
 
 from ..errors import Unsupported
 from ..kernels import ops
-from ..kernels.gemm import linear_act, linear_partial, linear_swiglu
+from ..kernels.gemm import linear_act, linear_geglu, linear_partial, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
 
@@ -28,8 +29,9 @@ class GatedMLP:
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
-        if spec.get("activation", "silu") != "silu":
-            raise Unsupported(f"gated_mlp: activation '{spec.get('activation')}' has no kernel (silu does)")
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise Unsupported(f"gated_mlp: activation '{self.activation}' has no kernel (silu and gelu_tanh do)")
         self.spec = spec
         self.rt = runtime
         self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
@@ -43,7 +45,10 @@ class GatedMLP:
         s, rt = self.spec, self.rt
         if x.shape[0] <= ops.SKINNY_FAST_ROWS:
             ops.stream_ahead(self.w_down)              # taken by the gate | up product, read by the product after it
-        act = linear_swiglu(x, self.w_gate_up, rt, s.inner)
+        if self.activation == "gelu_tanh":
+            act = linear_geglu(x, self.w_gate_up, rt, s.inner)
+        else:
+            act = linear_swiglu(x, self.w_gate_up, rt, s.inner)
         return linear_partial(act, self.w_down, rt, "ffn_out")
 
 
