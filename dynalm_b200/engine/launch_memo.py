@@ -125,7 +125,7 @@ class LayerLaunchMemo:
             tensors = owned_tensors(block)
             if cache is not None:
                 tensors = tensors + list(cache.arrays) + ([cache.block_table] if cache.block_table is not None else [])
-                if cache.state is not None:
+                if getattr(cache, "state", None) is not None:
                     tensors = tensors + list(cache.state.arrays)
             got = (cache, _Layout(tensors))
             self.layouts[index] = got

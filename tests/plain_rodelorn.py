@@ -110,7 +110,8 @@ class DeltaMixer:
     """The gated delta rule with short convolutions, unit-length queries and keys and a gated norm per head."""
 
     def __init__(self, m, t, p, eps):
-        self.H, self.G, self.d, self.e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        self.H, self.d = m["heads"], m["dim"]
+        self.G, self.e = m.get("kv_heads", self.H), m.get("vdim", self.d)
         self.eps = eps
         self.t = {k[len(p):]: v for k, v in t.items() if k.startswith(p)}
         self.cq, self.ck, self.cv = (ShortConv(self.t[n + ".conv"]) for n in "qkv")
@@ -149,7 +150,8 @@ class WindowAttention:
 
     def step(self, h, pos):
         m, t = self.m, self.t
-        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        H, d = m["heads"], m["dim"]
+        G, e, scale = m.get("kv_heads", H), m.get("vdim", d), m.get("scale", d ** -0.5)
         q = rms_norm(t["q"] @ h, self.eps, t["q.norm"]).reshape(H, d)
         k = rms_norm(t["k"] @ h, self.eps, t["k.norm"]).reshape(G, d)
         v = (t["v"] @ h).reshape(G, e)
@@ -167,7 +169,7 @@ class WindowAttention:
         out = np.zeros((H, e))
         for i in range(H):
             j = i // (H // G)
-            s = K[:, j] @ q[i] * m["scale"]
+            s = K[:, j] @ q[i] * scale
             p = np.exp(s - s.max())
             out[i] = (p / p.sum()) @ V[:, j]
         out = out.reshape(-1)
@@ -181,7 +183,7 @@ class GatedLinearRecurrence:
     softplus(lam)); S <- a S + sqrt(1 - a^2) i u; out = Wo (S y)."""
 
     def __init__(self, m, t, p):
-        self.B, self.R = m["blocks"], m["width"]
+        self.B, self.R = m.get("blocks", 1), m["width"]
         self.t = {k[len(p):]: v for k, v in t.items() if k.startswith(p)}
         self.conv = ShortConv(self.t["conv"], self.t["conv.b"])
         self.S = np.zeros(self.R)
@@ -225,9 +227,10 @@ class PlainRodelorn:
         mixers = []
         for i, layer in enumerate(self.cfg["layers"]):
             p = f"l{i}.mix."
-            if layer["type"] in ("delta", "delta_2"):
+            kind = layer["type"].rstrip("0123456789").rstrip("_")      # "delta_2": another instance of "delta"
+            if kind == "delta":
                 mixers.append(DeltaMixer(layer["mixer"], self.t, p, self.eps))
-            elif layer["type"] == "parallel":
+            elif kind == "parallel":
                 mixers.append(SideBySide(layer["mixer"], self.t, p, self.eps))
             else:
                 raise ValueError(layer["type"])
