@@ -382,9 +382,44 @@ def rematar_pair(name):
     return rematar, llama
 
 
+# --workload rodelorn: the Rodelorn design (gated delta rule layers, and windowed attention beside a gated linear
+# recurrence, in blocks that norm on both sides of every sublayer) beside Rematar, the closest design here (state-space
+# layers and windowed latent attention), at equal width, depth and feed-forward weights: a delta layer stands where a
+# state-space layer stands and a pair where an attention layer stands. Rodelorn's feed-forward is gated, Rematar's is
+# not and is 1.5 times as wide.
+RODELORN_SIZES = {
+    # name: (width, layer kinds (d: delta, p: pair), delta (heads, kv_heads, dim, vdim, taps),
+    #        attention (heads, kv_heads, dim, vdim, rot dims, window), recurrence (width, blocks, taps), ff, rematar size)
+    "w2048_d128": (2048, "dpdd", (16, 16, 128, 128, 4), (16, 4, 128, 128, 64, 1024), (2048, 16, 4), 8192, "w2048_n128"),
+    "w4096_d128": (4096, "dp", (32, 16, 128, 128, 4), (32, 8, 128, 128, 64, 2048), (4096, 32, 4), 14336, "w4096_n128"),
+    "w2048_d64": (2048, "dpdd", (32, 8, 64, 64, 4), (32, 8, 64, 64, 32, 512), (2048, 8, 4), 8192, "w2048_n64"),
+}
+
+
+def rodelorn_pair(name):
+    width, kinds, d, a, r, ff, rem = RODELORN_SIZES[name]
+    delta = {"heads": d[0], "kv_heads": d[1], "dim": d[2], "vdim": d[3], "conv": d[4]}
+    pair = {"left": {"heads": a[0], "kv_heads": a[1], "dim": a[2], "vdim": a[3], "scale": a[2] ** -0.5,
+                     "rot": {"base": 10000.0, "dims": a[4]}, "mask": {"size": a[5]}},
+            "right": {"width": r[0], "blocks": r[1], "conv": r[2]}, "left_scale": 1.0, "right_scale": 1.0}
+    rodelorn = {"architecture": "Rodelorn", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5},
+                "embedding": {"scale": 8.0}, "logit_scale": 0.25, "logit_softcap": 30.0,
+                "layers": [{"type": "delta" if k == "d" else "parallel", "mixer": dict(delta if k == "d" else pair),
+                            "mlp": {"kind": "dense", "ff": ff}} for k in kinds]}
+    _, _, s, la, l = REMATAR_SIZES[rem]
+    ssd = {"heads": s[0], "vdim": s[1], "state": s[2], "groups": s[3], "conv": s[4], "norm_groups": s[5]}
+    lat = {"heads": la[0], "dim": la[1], "rot_dim": la[2], "vdim": la[3], "q_rank": la[4], "kv_rank": la[5],
+           "scale": (la[1] + la[2]) ** -0.5, "rot": {"base": 10000.0, "dims": la[2]}, "mask": {"size": a[5]}}
+    rematar = {"architecture": "Rematar", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+               "embedding": {"scale": 8.0},
+               "layers": [{"type": "mamba2" if k == "d" else "latent_attention", "mixer": dict(ssd if k == "d" else lat),
+                           "mlp": {"kind": "dense", "ff": ff * 3 // 2}} for k in kinds]}
+    return rodelorn, rematar
+
+
 def arch_compare(args, kernels: bool, design: str = "todupel"):
-    """Prefill (one prompt of 2,048 tokens) and decode (batches of 8 and 64 holding 2,048 tokens each) of the Todupel design
-    and of the Llama shape of equal size, timed with CUDA events; with `kernels`, instead, the device time of every kernel
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 8 and 64 holding 2,048 tokens each) of a design
+    and of the model it is set beside (the Llama shape, or Rematar for Rodelorn) at equal size, timed with CUDA events; with `kernels`, instead, the device time of every kernel
     of one prefill step and of decode steps at batch 8 that run launch by launch. Prints one JSON line."""
     if kernels:
         os.environ["DYNALM_PDL"] = "0"          # every kernel's time its own: none starts beside the one in front of it
@@ -396,8 +431,9 @@ def arch_compare(args, kernels: bool, design: str = "todupel"):
 
     peaks = load_peaks()
     T, HELD_HERE, K = 2048, 2048, max(8, min(args.steps, 64))
-    sizes = ARCH_SIZES if design == "todupel" else REMATAR_SIZES
-    out = {"metric": f"{design.capitalize()} beside the Llama shape of equal size: prefill and decode tokens/s", "unit": "tokens/s",
+    sizes = {"todupel": ARCH_SIZES, "rematar": REMATAR_SIZES, "rodelorn": RODELORN_SIZES}[design]
+    other = "rematar" if design == "rodelorn" else "llama"
+    out = {"metric": f"{design.capitalize()} beside {'Rematar' if other == 'rematar' else 'the Llama shape'} of equal size: prefill and decode tokens/s", "unit": "tokens/s",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, random token ids", "peaks": peaks,
            "config": {"prefill_tokens": T, "decode_context": HELD_HERE, "decode_steps": K, "vocab": ARCH_VOCAB,
                       "l2": "inputs larger than L2: the weights of a model exceed 126 MB"}, "sizes": {}}
@@ -409,12 +445,17 @@ def arch_compare(args, kernels: bool, design: str = "todupel"):
                              "value_size": 2 * dim, "llama_head_dim": 2 * dim, "llama_intermediate": inter,
                              "todupel_ff": inter * 3 // 2}}
             pair = arch_pair(size)
-        else:
+        elif design == "rematar":
             width, kinds, s, a, l = REMATAR_SIZES[size]
             rec = {"shape": {"width": width, "layers": kinds, "ssd": list(s), "latent_attention": list(a), "llama": list(l),
                              "rematar_ff": l[3] * 3 // 2}}
             pair = rematar_pair(size)
-        for which, cfg in zip((design, "llama"), pair):
+        else:
+            width, kinds, d, a, r, ff, rem = RODELORN_SIZES[size]
+            rec = {"shape": {"width": width, "layers": kinds, "delta": list(d), "attention": list(a), "recurrence": list(r),
+                             "rodelorn_ff": ff, "rematar": rem, "rematar_ff": ff * 3 // 2}}
+            pair = rodelorn_pair(size)
+        for which, cfg in zip((design, other), pair):
             batches = (8,) if kernels else (8, 64)
             span = 16 + 3 * K + 64
             kv_tokens = max(batches) * (-(-(HELD_HERE + span) // 16) * 16) + 2 * T
@@ -488,9 +529,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels", "rematar", "rematar-kernels"] + sorted(SERVING), default="decode",
+    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels", "rematar", "rematar-kernels", "rodelorn", "rodelorn-kernels"] + sorted(SERVING), default="decode",
                     help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads; "
-                         "todupel / rematar: that design beside the Llama shape of equal size (todupel-kernels / rematar-kernels: per kernel)")
+                         "todupel / rematar: that design beside the Llama shape of equal size; rodelorn: that design beside Rematar of "
+                         "equal size (<design>-kernels: per kernel)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
     ap.add_argument("--no-serve", action="store_true", help="skip the points of the 3B and 8B serving workloads")
@@ -505,7 +547,7 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.workload in ("todupel", "todupel-kernels", "rematar", "rematar-kernels"):
+    if args.workload.split("-")[0] in ("todupel", "rematar", "rodelorn"):
         return arch_compare(args, kernels=args.workload.endswith("-kernels"), design=args.workload.split("-")[0])
     if args.workload != "decode":
         return serving(args.workload, args.layers if args.layers != FULL_LAYERS else None)

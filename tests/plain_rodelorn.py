@@ -278,3 +278,87 @@ class PlainRodelorn:
             if j + 1 < n:
                 x = self.token(state, nxt, len(prompt) + j)
         return out
+
+
+# --------------------------------------------------------------------------------------------
+# the same mechanisms over arrays of a whole sequence (for tests of one mechanism alone)
+# --------------------------------------------------------------------------------------------
+
+def causal_conv(x, taps, bias=None, in_bias=None):
+    """x: [n, C]; taps: [C, K], the last column the current token's; zeros before the start. in_bias joins every real
+    input before the taps (not the zeros in front)."""
+    conv = ShortConv(np.asarray(taps, dtype=np.float64), bias)
+    return np.stack([conv.step(row + in_bias if in_bias is not None else row) for row in np.asarray(x, dtype=np.float64)])
+
+
+def delta_rule_scan(q, k, v, b_raw, a_raw, a_log, dt_bias, S=None):
+    """q, k: [n, G, d] (after convolution and silu, not yet unit vectors); v: [n, H, e]; b_raw, a_raw: [n, H].
+    Returns o [n, H, e] and the last state [H, d, e]."""
+    n, G, d = q.shape
+    H, e = v.shape[1], v.shape[2]
+    S = np.zeros((H, d, e)) if S is None else S.copy()
+    out = np.zeros((n, H, e))
+    for t in range(n):
+        qt = q[t] / np.sqrt((q[t] * q[t]).sum(-1, keepdims=True) + 1e-6) * d ** -0.5
+        kt = k[t] / np.sqrt((k[t] * k[t]).sum(-1, keepdims=True) + 1e-6)
+        beta = sigmoid(b_raw[t])
+        g = np.exp(-np.exp(a_log) * softplus(a_raw[t] + dt_bias))
+        for h in range(H):
+            j = h // (H // G)
+            M = S[h] * g[h]
+            u = beta[h] * (v[t, h] - M.T @ kt[j])
+            S[h] = M + np.outer(kt[j], u)
+            out[t, h] = S[h].T @ qt[j]
+    return out, S
+
+
+def head_norm_gate(o, gate, weight, eps):
+    """o, gate: [n, H, e]; weight: [e]."""
+    return rms_norm(o, eps, weight) * silu(gate)
+
+
+def rglru_gates(u, ra, ra_b, ri, ri_b, lam, c=8.0):
+    """u: [n, R]; ra, ri: [B, out, in]; biases [B, R / B]. Returns the decay a and the gated input sqrt(1 - a^2) i u."""
+    n, R = u.shape
+    B = ra.shape[0]
+    ub = u.reshape(n, B, R // B)
+    r = sigmoid(np.einsum("boi,nbi->nbo", ra, ub) + ra_b).reshape(n, R)
+    i = sigmoid(np.einsum("boi,nbi->nbo", ri, ub) + ri_b).reshape(n, R)
+    a = np.exp(-c * r * softplus(lam))
+    return a, np.sqrt(1.0 - a * a) * i * u
+
+
+def linear_scan(a, m, S=None):
+    """S_t = a_t S_(t-1) + m_t from S (zeros when None), also for the first token. Returns every S_t."""
+    S = np.zeros(a.shape[1]) if S is None else S.copy()
+    out = np.zeros_like(a)
+    for t in range(a.shape[0]):
+        S = a[t] * S + m[t]
+        out[t] = S
+    return out
+
+
+def projection_norm_rotate(x, weight, eps, heads, positions, dims, base, factor):
+    """x: [n, heads * d]: one statistic over the whole row, plain weight, then the partial rotation per head."""
+    n = x.shape[0]
+    y = rms_norm(x, eps, weight).reshape(n, heads, -1) if weight is not None else x.reshape(n, heads, -1).copy()
+    if dims:
+        for t in range(n):
+            y[t] = rotate_half(y[t], positions[t], dims, base, factor)
+    return y
+
+
+def window_attention(q, keys, values, q_positions, scale, window):
+    """q: [n, H, d] at q_positions; keys [T, G, d], values [T, G, e] of positions 0..T-1. Position p sees
+    max(0, p - window + 1)..p (all of 0..p when window is 0)."""
+    n, H, _ = q.shape
+    G, e = keys.shape[1], values.shape[2]
+    out = np.zeros((n, H, e))
+    for t, p in enumerate(q_positions):
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(H):
+            j = h // (H // G)
+            s = keys[lo:p + 1, j] @ q[t, h] * scale
+            w = np.exp(s - s.max())
+            out[t, h] = (w / w.sum()) @ values[lo:p + 1, j]
+    return out
