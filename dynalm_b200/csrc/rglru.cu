@@ -7,8 +7,8 @@
 //
 // dl_rglru_gates works out a and m for every row (rows side by side: a block takes 8 rows of one part and walks the
 // part's two square matrices once for all of them; the matrices are given transposed, [part][in][out], so that
-// neighbouring threads read neighbouring weights). dl_rglru_scan carries S along every request's rows, one thread
-// per channel, from and into the request's state row.
+// neighbouring threads read neighbouring weights). dl_rglru_scan carries S along every request's rows, from and
+// into the request's state row, several runs of tokens of a channel side by side.
 #include "common.cuh"
 
 namespace dl {
@@ -64,24 +64,71 @@ rglru_gates_kernel(const T* __restrict__ u, const float* __restrict__ wa_t, cons
   }
 }
 
+// A block carries 32 channels of one request, its tokens in tiles of SC_SEGS x SC_LEN: thread (lane, seg) first folds
+// its SC_LEN tokens into one step (A, M) with S_after = A S_before + M, the block chains the SC_SEGS steps of a tile
+// from the state the tile began with, and every thread then runs its tokens again from the state its segment begins
+// with, writing the outputs. A tile costs one trip to global memory (every load is issued before the first use) and
+// 2 SC_LEN + SC_SEGS dependent multiply-adds instead of SC_SEGS x SC_LEN. Places past the request's end are the step
+// (1, 0), which changes nothing.
+constexpr int SC_SEGS = 8;
+constexpr int SC_LEN = 16;
+
 template <typename T>
-__global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ m, const T* __restrict__ y,
-                                  int y_stride, int y_col, const float* __restrict__ y_bias, float* __restrict__ state,
-                                  size_t state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                  T* __restrict__ out, int width) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
-  if (c >= width) return;
+__global__ void __launch_bounds__(32 * SC_SEGS)
+rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ m, const T* __restrict__ y,
+                  int y_stride, int y_col, const float* __restrict__ y_bias, float* __restrict__ state,
+                  size_t state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                  T* __restrict__ out, int width) {
+  __shared__ float sA[2][SC_SEGS][32], sM[2][SC_SEGS][32];
+  const int lane = threadIdx.x, seg = threadIdx.y;
+  const int c = blockIdx.x * 32 + lane, r = blockIdx.y;
+  const bool live = c < width;
   const int row0 = q_start[r], row1 = q_start[r + 1];
   float* sp = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + c;
-  float S = *sp;
-  const float by = y_bias ? y_bias[c] : 0.0f;
-  for (int row = row0; row < row1; ++row) {
-    const size_t at = static_cast<size_t>(row) * width + c;
-    S = fmaf(a[at], S, m[at]);
-    const float g = lru_gelu(to_float(y[static_cast<size_t>(row) * y_stride + y_col + c]) + by);
-    out[at] = from_float<T>(S * g);
+  float S0 = live ? *sp : 0.0f;
+  const float by = (y_bias && live) ? y_bias[c] : 0.0f;
+  int which = 0;
+  for (int base = row0; base < row1; base += SC_SEGS * SC_LEN, which ^= 1) {
+    const int first = base + seg * SC_LEN;
+    const int cnt = live ? max(0, min(SC_LEN, row1 - first)) : 0;
+    float av[SC_LEN], mv[SC_LEN], yv[SC_LEN];
+#pragma unroll
+    for (int i = 0; i < SC_LEN; ++i) {
+      av[i] = 1.0f;
+      mv[i] = 0.0f;
+      yv[i] = 0.0f;
+      if (i < cnt) {
+        const size_t at = static_cast<size_t>(first + i) * width + c;
+        av[i] = a[at];
+        mv[i] = m[at];
+        yv[i] = to_float(y[static_cast<size_t>(first + i) * y_stride + y_col + c]);
+      }
+    }
+    float A = 1.0f, M = 0.0f;
+#pragma unroll
+    for (int i = 0; i < SC_LEN; ++i) {
+      M = fmaf(av[i], M, mv[i]);
+      A *= av[i];
+    }
+    sA[which][seg][lane] = A;
+    sM[which][seg][lane] = M;
+    __syncthreads();                            // the other pair of tables is written next: one wait a tile is enough
+    float S = S0, mine = S0;
+#pragma unroll
+    for (int s = 0; s < SC_SEGS; ++s) {
+      if (s == seg) mine = S;
+      S = fmaf(sA[which][s][lane], S, sM[which][s][lane]);
+    }
+    S0 = S;
+#pragma unroll
+    for (int i = 0; i < SC_LEN; ++i) {
+      if (i < cnt) {
+        mine = fmaf(av[i], mine, mv[i]);
+        out[static_cast<size_t>(first + i) * width + c] = from_float<T>(mine * lru_gelu(yv[i] + by));
+      }
+    }
   }
-  *sp = S;
+  if (seg == 0 && live) *sp = S0;
 }
 
 }  // namespace dl
@@ -121,8 +168,8 @@ DL_EXPORT int dl_rglru_scan(int dtype, const float* a, const float* m, const voi
                             const int* state_slots, void* out, int requests, int width, cudaStream_t stream) {
   if (requests <= 0 || width <= 0) return 0;
   if (requests > 65535) return DL_ERR_UNSUPPORTED;
-  const int threads = 128;
-  dim3 grid((width + threads - 1) / threads, requests);
+  const dim3 threads(32, dl::SC_SEGS);
+  dim3 grid((width + 31) / 32, requests);
   if (dtype == 0) dl::rglru_scan_kernel<float><<<grid, threads, 0, stream>>>(a, m, static_cast<const float*>(y), y_stride, y_col, y_bias, state, static_cast<size_t>(state_stride), q_start, state_slots, static_cast<float*>(out), width);
   else if (dtype == 1) dl::rglru_scan_kernel<dl::bf16><<<grid, threads, 0, stream>>>(a, m, static_cast<const dl::bf16*>(y), y_stride, y_col, y_bias, state, static_cast<size_t>(state_stride), q_start, state_slots, static_cast<dl::bf16*>(out), width);
   else return DL_ERR_UNSUPPORTED;

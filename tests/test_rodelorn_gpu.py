@@ -18,7 +18,10 @@ from rodelorn_configs import RODELORN
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
-TOL = {"float32": (2e-5, 2e-5), "bfloat16": (3e-2, 2e-2)}      # (absolute, relative to the row's largest logit)
+# float32: (absolute, relative to the row's largest logit) on every logit. bfloat16: the spread of a row's difference
+# against the spread of its logits; rounding alone gives 0.015 to 0.02 in the middle and 0.08 at the worst row here.
+TOL = {"float32": (2e-5, 2e-5), "bfloat16": (0.0, 0.12)}
+SPREAD = {"float32": False, "bfloat16": True}
 LENGTHS = {"oa": [5, 70, 150, 33, 260, 129], "ob": [1, 7, 64, 100, 129, 40], "oc": [3, 48, 95, 200, 16, 131]}
 SIZES = [16, 7, 2, 5, 3, 2, 11, 32, 2, 9, 64, 2]
 
@@ -483,7 +486,7 @@ def test_replay_all_cuts(name, dtype, folders, plain_logits):
         need = plan.max_live_tokens(64)          # just what the plan needs: pages of finished requests are used again
         built = _built(folders[dtype][name], dtype, need, max(need, 64), max_requests=4)
         got = run_plan_in_process(built.step_fn, plan)
-        compare(plan, got, logits, tol[0], tol[1], f"{name}/{dtype}/{what}")
+        compare(plan, got, logits, tol[0], tol[1], f"{name}/{dtype}/{what}", spread=SPREAD[dtype])
         assert built.cache.free_pages == built.cache.num_pages, "pages were lost"
 
 
@@ -525,7 +528,7 @@ def test_many_single_token_rows_beside_a_portion(dtype, folders):
     need = plan.max_live_tokens(64)
     built = _built(folders[dtype][name], dtype, need, 256, max_requests=24)
     got = run_plan_in_process(built.step_fn, plan)
-    compare(plan, got, logits, *TOL[dtype], f"{name}/{dtype}/many rows")
+    compare(plan, got, logits, *TOL[dtype], f"{name}/{dtype}/many rows", spread=SPREAD[dtype])
 
 
 @pytest.mark.parametrize("name", ["oa", "oc"])
