@@ -13,9 +13,10 @@
 // A column of S lies over P neighbouring lanes of a computing warp, lane p holding the R rows p R .. p R + R - 1 in
 // registers; the two dot products of a token are finished by shuffles among those lanes. A request's tokens are
 // walked in tiles of 16 held twice in shared memory: while the computing warps run a tile's tokens over their
-// registers, the fetching warps bring the next tile in (queries and keys made unit vectors, a warp per token; the
-// values of the block's columns; the two gates), so no token waits for global memory. Within a token only
-// g S . k, its shuffles and the rank-one update lie on the path to the next token; the read-out S . q does not.
+// registers, the fetching warps write the next tile (queries and keys made unit vectors, a warp per token; the
+// values of the block's columns; the two gates; k . q) and ask for the one after it, whose numbers then have a whole
+// tile's time to arrive in their registers: no token waits for global memory. Both dot products of a
+// token run over the state it found (S'^T q = g S^T q + u (k . q)), so one round of shuffles a token is enough.
 // A lane's rows are R + 4 floats apart in shared memory, so that the P lanes' 16-byte loads fall into different banks.
 //
 // dl_head_norm_gate: out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * silu(gate[t, h, :]).
@@ -34,77 +35,107 @@ struct DrTile {
   static constexpr int RS = R + 4;                      // floats between two lanes' rows
   static constexpr int TS = P * RS;                     // floats of one token's query (or key)
   static constexpr int COLS = DR_COMPUTE / P;
-  static constexpr int FLOATS = 2 * DR_TT * TS + DR_TT * COLS + 2 * DR_TT;      // q | k | v | g | beta
+  static constexpr int FLOATS = 2 * DR_TT * TS + DR_TT * COLS + 4 * DR_TT;      // q | k | v | g | beta | k.q | spare
 };
 
-// The fetching warps: tile [t0, t0 + tn) of the request's rows into one of the two buffers.
+// What a fetching thread holds of one tile between asking for it and writing it to shared memory.
 template <typename T, int R, int P>
-__device__ __forceinline__ void dr_fetch(float* buf, const T* __restrict__ u, int u_stride, int q_at, int k_at, int v_at,
-                                         const T* __restrict__ proj, int proj_stride, int b_at, int a_at, int first_row,
-                                         int tn, int d, int e, int col0, float q_scale, float decay_rate, float bias, int lt) {
+struct DrRaw {
+  static constexpr int NT = DR_TT / 4;                  // tokens of a warp
+  static constexpr int NL = (R * P + 31) / 32;          // a lane's numbers of one query (or key)
+  static constexpr int NV = DR_TT * DrTile<R, P>::COLS / (DR_THREADS - DR_COMPUTE);
+  T q[NT][NL], k[NT][NL], v[NV], b, a;                  // as they lie in memory: nothing waits for a load before the tile is written
+};
+
+// The fetching warps ask for tile [first_row, first_row + tn) of the request's rows: every load is issued, none is
+// waited for. The tile is asked for one tile's time before it is written, so its numbers are there by then.
+template <typename T, int R, int P>
+__device__ __forceinline__ void dr_ask(DrRaw<T, R, P>& raw, const T* __restrict__ u, int u_stride, int q_at, int k_at,
+                                       int v_at, const T* __restrict__ proj, int proj_stride, int b_at, int a_at,
+                                       int first_row, int tn, int d, int e, int col0, int lt) {
   using L = DrTile<R, P>;
+  using W = DrRaw<T, R, P>;
+  const int lane = lt & 31, warp = lt >> 5;
+  const T zero = from_float<T>(0.0f);
+#pragma unroll
+  for (int s = 0; s < W::NT; ++s) {
+    const int tt = warp + 4 * s;
+    const T* urow = u + static_cast<size_t>(first_row + max(min(tt, tn - 1), 0)) * u_stride;
+#pragma unroll
+    for (int c = 0; c < W::NL; ++c) {
+      const int i = lane + 32 * c;
+      const bool ok = tt < tn && i < d;
+      raw.q[s][c] = ok ? urow[q_at + i] : zero;
+      raw.k[s][c] = ok ? urow[k_at + i] : zero;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < W::NV; ++c) {
+    const int idx = lt + (DR_THREADS - DR_COMPUTE) * c;
+    const int tt = idx / L::COLS, col = col0 + idx % L::COLS;
+    raw.v[c] = (tt < tn && col < e) ? u[static_cast<size_t>(first_row + tt) * u_stride + v_at + col] : zero;
+  }
+  raw.b = zero;
+  raw.a = zero;
+  if (lt < tn) {
+    const T* prow = proj + static_cast<size_t>(first_row + lt) * proj_stride;
+    raw.b = prow[b_at];
+    raw.a = prow[a_at];
+  }
+}
+
+// ... and write it into one of the two buffers: queries and keys as unit vectors (a warp per token), k . q, the
+// values of the block's columns, the two gates.
+template <typename T, int R, int P>
+__device__ __forceinline__ void dr_put(const DrRaw<T, R, P>& raw, float* buf, int tn, int d, float q_scale, float decay_rate,
+                                       float bias, int lt) {
+  using L = DrTile<R, P>;
+  using W = DrRaw<T, R, P>;
   float* sq = buf;
   float* sk = sq + DR_TT * L::TS;
   float* sv = sk + DR_TT * L::TS;
   float* sg = sv + DR_TT * L::COLS;
   float* sbeta = sg + DR_TT;
+  float* skq = sbeta + DR_TT;
   const int lane = lt & 31, warp = lt >> 5;
-  constexpr int NT = DR_TT / 4;                         // tokens of a warp
-  constexpr int NL = (R * P + 31) / 32;                 // a lane's numbers of one query (or key)
-  constexpr int NV = DR_TT * L::COLS / (DR_THREADS - DR_COMPUTE);
-  // every load of the tile is issued before the first one is used
-  float qv[NT][NL], kv[NT][NL], vv[NV], raw_b = 0.0f, raw_a = 0.0f;
 #pragma unroll
-  for (int s = 0; s < NT; ++s) {
+  for (int s = 0; s < W::NT; ++s) {
     const int tt = warp + 4 * s;
-    const T* urow = u + static_cast<size_t>(first_row + max(min(tt, tn - 1), 0)) * u_stride;
+    float qq = 0.0f, kk = 0.0f, kq = 0.0f, qf[W::NL], kf[W::NL];
 #pragma unroll
-    for (int c = 0; c < NL; ++c) {
-      const int i = lane + 32 * c;
-      const bool ok = tt < tn && i < d;
-      qv[s][c] = ok ? to_float(urow[q_at + i]) : 0.0f;
-      kv[s][c] = ok ? to_float(urow[k_at + i]) : 0.0f;
+    for (int c = 0; c < W::NL; ++c) {
+      qf[c] = to_float(raw.q[s][c]);
+      kf[c] = to_float(raw.k[s][c]);
+      qq = fmaf(qf[c], qf[c], qq);
+      kk = fmaf(kf[c], kf[c], kk);
+      kq = fmaf(kf[c], qf[c], kq);
     }
-  }
 #pragma unroll
-  for (int c = 0; c < NV; ++c) {
-    const int idx = lt + (DR_THREADS - DR_COMPUTE) * c;
-    const int tt = idx / L::COLS, col = col0 + idx % L::COLS;
-    vv[c] = (tt < tn && col < e) ? to_float(u[static_cast<size_t>(first_row + tt) * u_stride + v_at + col]) : 0.0f;
-  }
-  if (lt < tn) {
-    const T* prow = proj + static_cast<size_t>(first_row + lt) * proj_stride;
-    raw_b = to_float(prow[b_at]);
-    raw_a = to_float(prow[a_at]);
-  }
-#pragma unroll
-  for (int s = 0; s < NT; ++s) {
-    const int tt = warp + 4 * s;
-    float qq = 0.0f, kk = 0.0f;
-#pragma unroll
-    for (int c = 0; c < NL; ++c) {
-      qq = fmaf(qv[s][c], qv[s][c], qq);
-      kk = fmaf(kv[s][c], kv[s][c], kk);
+    for (int o = 16; o > 0; o >>= 1) {                  // three sums side by side
+      qq += __shfl_xor_sync(0xffffffffu, qq, o);
+      kk += __shfl_xor_sync(0xffffffffu, kk, o);
+      kq += __shfl_xor_sync(0xffffffffu, kq, o);
     }
-    const float fq = q_scale / sqrtf(warp_sum(qq) + 1e-6f), fk = 1.0f / sqrtf(warp_sum(kk) + 1e-6f);
+    const float fq = q_scale / sqrtf(qq + 1e-6f), fk = 1.0f / sqrtf(kk + 1e-6f);
+    if (lane == 0 && tt < tn) skq[tt] = kq * fq * fk;   // the unit key times the scaled unit query
 #pragma unroll
-    for (int c = 0; c < NL; ++c) {
+    for (int c = 0; c < W::NL; ++c) {
       const int i = lane + 32 * c;
       if (tt < tn && i < d) {
         const int at = tt * L::TS + (i / R) * L::RS + i % R;
-        sq[at] = qv[s][c] * fq;
-        sk[at] = kv[s][c] * fk;
+        sq[at] = qf[c] * fq;
+        sk[at] = kf[c] * fk;
       }
     }
   }
 #pragma unroll
-  for (int c = 0; c < NV; ++c) {
+  for (int c = 0; c < W::NV; ++c) {
     const int idx = lt + (DR_THREADS - DR_COMPUTE) * c;
-    if (idx < tn * L::COLS) sv[idx] = vv[c];
+    if (idx < tn * L::COLS) sv[idx] = to_float(raw.v[c]);
   }
   if (lt < tn) {
-    sbeta[lt] = 1.0f / (1.0f + expf(-raw_b));
-    sg[lt] = expf(-decay_rate * dr_softplus(raw_a + bias));
+    sbeta[lt] = 1.0f / (1.0f + expf(-to_float(raw.b)));
+    sg[lt] = expf(-decay_rate * dr_softplus(to_float(raw.a) + bias));
   }
 }
 
@@ -137,6 +168,8 @@ delta_rule_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, i
   const bool live = computes && col < e;
   float* S_g = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + static_cast<size_t>(h) * d * e;
   float S[R];
+  DrRaw<T, R, P> raw;
+  const int lt = tid - DR_COMPUTE;
   if (computes) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -144,8 +177,11 @@ delta_rule_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, i
       S[i] = (live && row < d) ? S_g[static_cast<size_t>(row) * e + col] : 0.0f;
     }
   } else {
-    dr_fetch<T, R, P>(sm, u, u_stride, q_at, k_at, v_at, proj, proj_stride, b_at, a_at, row0, min(DR_TT, n), d, e, col0,
-                      q_scale, decay_rate, bias, tid - DR_COMPUTE);
+    dr_ask<T, R, P>(raw, u, u_stride, q_at, k_at, v_at, proj, proj_stride, b_at, a_at, row0, min(DR_TT, n), d, e, col0, lt);
+    dr_put<T, R, P>(raw, sm, min(DR_TT, n), d, q_scale, decay_rate, bias, lt);
+    if (n > DR_TT)
+      dr_ask<T, R, P>(raw, u, u_stride, q_at, k_at, v_at, proj, proj_stride, b_at, a_at, row0 + DR_TT,
+                      min(DR_TT, n - DR_TT), d, e, col0, lt);
   }
   __syncthreads();
 
@@ -153,10 +189,13 @@ delta_rule_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, i
   for (int t0 = 0; t0 < n; t0 += DR_TT, which ^= 1) {
     const int tn = min(DR_TT, n - t0);
     if (!computes) {
-      if (t0 + DR_TT < n)
-        dr_fetch<T, R, P>(sm + (which ^ 1) * L::FLOATS, u, u_stride, q_at, k_at, v_at, proj, proj_stride, b_at, a_at,
-                          row0 + t0 + DR_TT, min(DR_TT, n - t0 - DR_TT), d, e, col0, q_scale, decay_rate, bias,
-                          tid - DR_COMPUTE);
+      // the tile after this one was asked for a tile ago: write it, then ask for the one after it
+      if (t0 + DR_TT < n) {
+        dr_put<T, R, P>(raw, sm + (which ^ 1) * L::FLOATS, min(DR_TT, n - t0 - DR_TT), d, q_scale, decay_rate, bias, lt);
+        if (t0 + 2 * DR_TT < n)
+          dr_ask<T, R, P>(raw, u, u_stride, q_at, k_at, v_at, proj, proj_stride, b_at, a_at, row0 + t0 + 2 * DR_TT,
+                          min(DR_TT, n - t0 - 2 * DR_TT), d, e, col0, lt);
+      }
     } else {
       const float* sq = sm + which * L::FLOATS;
       const float* sk = sq + DR_TT * L::TS;
@@ -164,63 +203,43 @@ delta_rule_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, i
       const float* sg = sv + DR_TT * L::COLS;
       const float* sbeta = sg + DR_TT;
       float* orow = out + static_cast<size_t>(row0 + t0) * (H * e) + h * e + col;
-      // A token's key is in registers before its turn comes (fetched under the token before it), its query is
-      // fetched under the shuffles of the first dot product.
-      float kr[R];
-      {
-        const float4* k4 = reinterpret_cast<const float4*>(sk + part * L::RS);
-#pragma unroll
-        for (int i = 0; i < R / 4; ++i) {
-          const float4 kv = k4[i];
-          kr[4 * i] = kv.x; kr[4 * i + 1] = kv.y; kr[4 * i + 2] = kv.z; kr[4 * i + 3] = kv.w;
-        }
-      }
-      float g = sg[0], beta = sbeta[0], v = sv[tid / P];
+      const float* skq = sbeta + DR_TT;
+      // Both dot products of a token run over the state the token found: with S' = g S + k u^T the read-out is
+      // S'^T q = g (S^T q) + u (k . q), and k . q is the same for every column (the fetching warps leave it beside
+      // the gates). So the path from token to token is one round of multiply-adds, one round of shuffles (both sums
+      // at once) and the update; the products g S do not wait for the shuffles.
 #pragma unroll 2
       for (int tt = 0; tt < tn; ++tt) {
-        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < R / 4; ++i) {
-          S[4 * i] *= g; S[4 * i + 1] *= g; S[4 * i + 2] *= g; S[4 * i + 3] *= g;
-          d0 = fmaf(S[4 * i], kr[4 * i], d0);
-          d1 = fmaf(S[4 * i + 1], kr[4 * i + 1], d1);
-          d2 = fmaf(S[4 * i + 2], kr[4 * i + 2], d2);
-          d3 = fmaf(S[4 * i + 3], kr[4 * i + 3], d3);
-        }
-        float dot = (d0 + d1) + (d2 + d3);
+        const float g = sg[tt], beta = sbeta[tt], kq = skq[tt], v = sv[tt * L::COLS + tid / P];
+        const float4* k4 = reinterpret_cast<const float4*>(sk + tt * L::TS + part * L::RS);
         const float4* q4 = reinterpret_cast<const float4*>(sq + tt * L::TS + part * L::RS);
-        float qr[R];
+        float kr[R];
+        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
         for (int i = 0; i < R / 4; ++i) {
-          const float4 qv = q4[i];
-          qr[4 * i] = qv.x; qr[4 * i + 1] = qv.y; qr[4 * i + 2] = qv.z; qr[4 * i + 3] = qv.w;
-        }
-#pragma unroll
-        for (int o = P >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float uval = beta * (v - dot);
-        const int nx = min(tt + 1, DR_TT - 1);            // the last token of a tile fetches its own key again
-        const float4* k4 = reinterpret_cast<const float4*>(sk + nx * L::TS + part * L::RS);
-        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < R / 4; ++i) {
-          S[4 * i] = fmaf(kr[4 * i], uval, S[4 * i]);
-          S[4 * i + 1] = fmaf(kr[4 * i + 1], uval, S[4 * i + 1]);
-          S[4 * i + 2] = fmaf(kr[4 * i + 2], uval, S[4 * i + 2]);
-          S[4 * i + 3] = fmaf(kr[4 * i + 3], uval, S[4 * i + 3]);
-          const float4 kv = k4[i];
+          const float4 kv = k4[i], qv = q4[i];
           kr[4 * i] = kv.x; kr[4 * i + 1] = kv.y; kr[4 * i + 2] = kv.z; kr[4 * i + 3] = kv.w;
-          o0 = fmaf(S[4 * i], qr[4 * i], o0);
-          o1 = fmaf(S[4 * i + 1], qr[4 * i + 1], o1);
-          o2 = fmaf(S[4 * i + 2], qr[4 * i + 2], o2);
-          o3 = fmaf(S[4 * i + 3], qr[4 * i + 3], o3);
+          d0 = fmaf(S[4 * i], kv.x, d0);
+          d1 = fmaf(S[4 * i + 1], kv.y, d1);
+          d2 = fmaf(S[4 * i + 2], kv.z, d2);
+          d3 = fmaf(S[4 * i + 3], kv.w, d3);
+          o0 = fmaf(S[4 * i], qv.x, o0);
+          o1 = fmaf(S[4 * i + 1], qv.y, o1);
+          o2 = fmaf(S[4 * i + 2], qv.z, o2);
+          o3 = fmaf(S[4 * i + 3], qv.w, o3);
         }
-        g = sg[nx];
-        beta = sbeta[nx];
-        v = sv[nx * L::COLS + tid / P];
-        float oq = (o0 + o1) + (o2 + o3);
+        float dot = (d0 + d1) + (d2 + d3), sq_dot = (o0 + o1) + (o2 + o3);
 #pragma unroll
-        for (int o = P >> 1; o > 0; o >>= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-        if (live && part == 0) orow[static_cast<size_t>(tt) * (H * e)] = oq;
+        for (int i = 0; i < R; ++i) S[i] *= g;
+#pragma unroll
+        for (int o = P >> 1; o > 0; o >>= 1) {
+          dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          sq_dot += __shfl_xor_sync(0xffffffffu, sq_dot, o);
+        }
+        const float uval = beta * (v - g * dot);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], uval, S[i]);
+        if (live && part == 0) orow[static_cast<size_t>(tt) * (H * e)] = fmaf(uval, kq, g * sq_dot);
       }
     }
     __syncthreads();                            // the tile has been read, the next one is whole
@@ -285,11 +304,13 @@ DL_EXPORT int dl_delta_rule(int dtype, const void* u, int u_stride, int q_col, i
   if (H <= 0 || G <= 0 || H % G != 0 || d <= 0 || e <= 0 || d > 512 || H > 65535 || requests > 65535 ||
       (dtype != 0 && dtype != 1))
     return DL_ERR_UNSUPPORTED;
-  // lanes per column: the fewest (a power of two up to 8) that leave a lane at most 32 rows, or 64 from d = 257 on
+  // lanes per column: the fewest (a power of two up to 16) that leave a lane at most 16 rows, or up to 32 from d = 257 on.
+  // Short rows keep a token's chain of dependent multiply-adds short; the shuffles that finish a dot product grow
+  // by one step with every doubling.
   int P = 1;
-  while (P < 8 && (d + P - 1) / P > 32) P *= 2;
+  while (P < 16 && (d + P - 1) / P > 16) P *= 2;
   const int need = (d + P - 1) / P;
-  const int R = need > 32 ? 64 : (need + 7) / 8 * 8;
+  const int R = (need + 7) / 8 * 8;
 #define DL_DR(RR, PP)                                                                                                      \
   if (R == RR && P == PP)                                                                                                  \
     return dtype == 0 ? dl::delta_rule_launch<float, RR, PP>(u, u_stride, q_col, k_col, v_col, proj, proj_stride, b_col,   \
@@ -298,10 +319,9 @@ DL_EXPORT int dl_delta_rule(int dtype, const void* u, int u_stride, int q_col, i
                       : dl::delta_rule_launch<dl::bf16, RR, PP>(u, u_stride, q_col, k_col, v_col, proj, proj_stride,       \
                                                                 b_col, a_col, a_log, dt_bias, state, state_stride,         \
                                                                 q_start, state_slots, out, requests, H, G, d, e, stream)
-  DL_DR(8, 1); DL_DR(16, 1); DL_DR(24, 1); DL_DR(32, 1);       // d up to 32
-  DL_DR(24, 2); DL_DR(32, 2);                                  // 33 .. 64
-  DL_DR(24, 4); DL_DR(32, 4);                                  // 65 .. 128
-  DL_DR(24, 8); DL_DR(32, 8); DL_DR(64, 8);                    // 129 .. 512
+  DL_DR(8, 1); DL_DR(16, 1);                                   // d up to 16
+  DL_DR(16, 2); DL_DR(16, 4); DL_DR(16, 8); DL_DR(16, 16);     // 17 .. 32, .. 64, .. 128, .. 256
+  DL_DR(24, 16); DL_DR(32, 16);                                // 257 .. 512
 #undef DL_DR
   return DL_ERR_UNSUPPORTED;
 }
