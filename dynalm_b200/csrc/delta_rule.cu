@@ -253,6 +253,95 @@ delta_rule_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, i
   }
 }
 
+// Steps of single tokens (decoding): what counts is the state's trip through memory, H d e floats read and written a
+// request. Block = (32 columns, head, request), 128 threads as 32 columns x 4 runs of rows, so that a warp reads 128
+// bytes of a state row at once and many light blocks share an SM. The block's slice of S waits in shared memory
+// between the two dot products and the update. A request that brought several tokens is walked token by token
+// (correct, not fast: the host sends such steps to the tiled kernel above); one that brought none is left alone.
+constexpr int DS_COLS = 32;
+constexpr int DS_RUNS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(DS_COLS * DS_RUNS)
+delta_rule_step_kernel(const T* __restrict__ u, int u_stride, int q_col, int k_col, int v_col,
+                       const T* __restrict__ proj, int proj_stride, int b_col, int a_col,
+                       const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                       float* __restrict__ state, size_t state_stride, const int* __restrict__ q_start,
+                       const int* __restrict__ state_slots, float* __restrict__ out, int H, int G, int d, int e) {
+  extern __shared__ __align__(16) float sm[];
+  float* sS = sm;                               // [d][DS_COLS]
+  float* sk = sS + static_cast<size_t>(d) * DS_COLS;      // [d]
+  float* sq = sk + d;                           // [d]
+  float* part = sq + d;                         // [2][DS_RUNS][DS_COLS]
+  __shared__ float red[33];
+  const int h = blockIdx.y, r = blockIdx.z;
+  const int j = h / (H / G);
+  const int tid = threadIdx.x, c = tid % DS_COLS, run = tid / DS_COLS;
+  const int col = blockIdx.x * DS_COLS + c;
+  const bool live = col < e;
+  const int row0 = q_start[r], row1 = q_start[r + 1];
+  if (row1 <= row0) return;
+  float* S_g = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + static_cast<size_t>(h) * d * e;
+  const float q_scale = rsqrtf(static_cast<float>(d));
+  const float decay_rate = expf(a_log[h]), bias = dt_bias[h];
+  for (int row = row0; row < row1; ++row) {
+    const T* urow = u + static_cast<size_t>(row) * u_stride;
+    float qq = 0.0f, kk = 0.0f, kq = 0.0f;
+    for (int i = tid; i < d; i += DS_COLS * DS_RUNS) {
+      const float a = to_float(urow[q_col + j * d + i]), b = to_float(urow[k_col + j * d + i]);
+      sq[i] = a;
+      sk[i] = b;
+      qq = fmaf(a, a, qq);
+      kk = fmaf(b, b, kk);
+      kq = fmaf(a, b, kq);
+    }
+    float dot = 0.0f, rd = 0.0f;
+    if (row == row0) {                          // the state comes in under the three sums
+#pragma unroll 8
+      for (int i = run; i < d; i += DS_RUNS) sS[i * DS_COLS + c] = live ? S_g[static_cast<size_t>(i) * e + col] : 0.0f;
+    }
+    qq = block_sum(qq, red);
+    kk = block_sum(kk, red);
+    kq = block_sum(kq, red);
+    const float fq = q_scale / sqrtf(qq + 1e-6f), fk = 1.0f / sqrtf(kk + 1e-6f);
+    const T* prow = proj + static_cast<size_t>(row) * proj_stride;
+    const float beta = 1.0f / (1.0f + expf(-to_float(prow[b_col + h])));
+    const float g = expf(-decay_rate * dr_softplus(to_float(prow[a_col + h]) + bias));
+    const float v = live ? to_float(urow[v_col + h * e + col]) : 0.0f;
+#pragma unroll 8
+    for (int i = run; i < d; i += DS_RUNS) {
+      const float s = sS[i * DS_COLS + c];
+      dot = fmaf(s, sk[i], dot);
+      rd = fmaf(s, sq[i], rd);
+    }
+    part[run * DS_COLS + c] = dot;
+    part[(DS_RUNS + run) * DS_COLS + c] = rd;
+    __syncthreads();
+    dot = 0.0f;
+    rd = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DS_RUNS; ++w) {
+      dot += part[w * DS_COLS + c];
+      rd += part[(DS_RUNS + w) * DS_COLS + c];
+    }
+    // with S' = g S + k u^T:  S'^T q = g S^T q + u (k . q)
+    const float uval = beta * (v - g * fk * dot);
+    if (live && run == 0) out[static_cast<size_t>(row) * (H * e) + h * e + col] = fmaf(uval, kq * fq * fk, g * fq * rd);
+    const float ku = uval * fk;
+    const bool last = row + 1 == row1;
+#pragma unroll 8
+    for (int i = run; i < d; i += DS_RUNS) {
+      const float s = fmaf(sk[i], ku, g * sS[i * DS_COLS + c]);
+      if (last) {
+        if (live) S_g[static_cast<size_t>(i) * e + col] = s;
+      } else {
+        sS[i * DS_COLS + c] = s;
+      }
+    }
+    __syncthreads();                            // sk, sq and the partial sums are free again
+  }
+}
+
 // One warp per (row, head).
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride, int gate_col,
@@ -324,6 +413,35 @@ DL_EXPORT int dl_delta_rule(int dtype, const void* u, int u_stride, int q_col, i
   DL_DR(24, 16); DL_DR(32, 16);                                // 257 .. 512
 #undef DL_DR
   return DL_ERR_UNSUPPORTED;
+}
+
+// The same step for batches of single tokens: the same arguments, any d.
+DL_EXPORT int dl_delta_rule_step(int dtype, const void* u, int u_stride, int q_col, int k_col, int v_col, const void* proj,
+                                 int proj_stride, int b_col, int a_col, const float* a_log, const float* dt_bias,
+                                 float* state, long long state_stride, const int* q_start, const int* state_slots,
+                                 float* out, int requests, int H, int G, int d, int e, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G != 0 || d <= 0 || e <= 0 || H > 65535 || requests > 65535 || (dtype != 0 && dtype != 1))
+    return DL_ERR_UNSUPPORTED;
+  const size_t smem = (static_cast<size_t>(d) * dl::DS_COLS + 2 * d + 2 * dl::DS_RUNS * dl::DS_COLS) * sizeof(float);
+  if (smem > 200 * 1024) return DL_ERR_UNSUPPORTED;
+  dim3 grid((e + dl::DS_COLS - 1) / dl::DS_COLS, H, requests);
+#define DL_DS(T)                                                                                                        \
+  do {                                                                                                                  \
+    auto kernel = dl::delta_rule_step_kernel<T>;                                                                        \
+    if (smem > 48 * 1024) {                                                                                             \
+      const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+      if (err != cudaSuccess) return static_cast<int>(err);                                                             \
+    }                                                                                                                   \
+    kernel<<<grid, dl::DS_COLS * dl::DS_RUNS, smem, stream>>>(static_cast<const T*>(u), u_stride, q_col, k_col, v_col,  \
+                                                              static_cast<const T*>(proj), proj_stride, b_col, a_col,   \
+                                                              a_log, dt_bias, state, static_cast<size_t>(state_stride), \
+                                                              q_start, state_slots, out, H, G, d, e);                   \
+  } while (0)
+  if (dtype == 0) DL_DS(float);
+  else DL_DS(dl::bf16);
+#undef DL_DS
+  return dl::launch_status();
 }
 
 // o: float32 contiguous [rows, H * e]; gate: rows of gate_stride elements, the gate of head h at gate_col + h * e;

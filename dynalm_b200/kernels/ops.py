@@ -70,6 +70,7 @@ _SIGNATURES = {
                                           _P]},
     "delta_rule": {
         "dl_delta_rule": [_I, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "dl_delta_rule_step": [_I, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "dl_head_norm_gate": [_I, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _P]},
     "rglru": {
         "dl_rglru_gates": [_I, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
@@ -1672,7 +1673,9 @@ def delta_rule(u: torch.Tensor, q_col: int, k_col: int, v_col: int, proj: torch.
     if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (u.shape[0], heads * vdim):
         raise InvalidArgument("delta_rule: out float32 contiguous [rows, H*e]")
     check_limits("delta_rule", requests=state.shape[0], rows=u.shape[0])
-    _check(_fn("delta_rule", "dl_delta_rule")(dtype_code(u.dtype), _p(u), u.stride(0), q_col, k_col, v_col, _p(proj),
+    # a step of single tokens goes to the light kernel that is bound by the state's trip through memory alone
+    entry = "dl_delta_rule_step" if u.shape[0] <= requests else "dl_delta_rule"
+    _check(_fn("delta_rule", entry)(dtype_code(u.dtype), _p(u), u.stride(0), q_col, k_col, v_col, _p(proj),
                                                proj.stride(0), b_col, a_col, _p(a_log), _p(dt_bias), _p(state),
                                                state.stride(0), _p(q_start), _p(state_slots), _p(out), requests, heads,
                                                kv_heads, dim, vdim, _stream()), "delta_rule")
