@@ -235,6 +235,44 @@ def test_delta_rule_reads_what_the_token_wrote():
     _close(_np(o[0]), _np(v) / np.sqrt(d), 1e-5, "read-out after the write")
 
 
+@pytest.mark.parametrize("H,G,d,e", [(3, 1, 20, 12), (2, 2, 128, 40), (4, 2, 48, 70)])
+def test_delta_rule_steps_of_single_tokens(H, G, d, e):
+    """Steps with no more rows than requests take the kernel for single tokens: three requests decode side by side
+    from states that a prompt left, then a step in which one request brings nothing and another brings two tokens
+    (as many rows as requests all the same), against the plain rule over each whole sequence."""
+    from dynalm_b200.kernels import ops
+    rng = np.random.RandomState(d + e)
+    qk, inner = G * d, H * e
+    a_log, dt_bias = rng.randn(H) * 0.3, rng.randn(H) * 0.3
+    a_log[0] = -7.0
+    n, prompt = 14, 5
+    seqs, want = {}, {}
+    for s in (0, 2, 3):
+        seqs[s] = _delta_inputs(rng, n, H, G, d, e, torch.float32)
+        u, ba = seqs[s]
+        want[s], _ = plain.delta_rule_scan(u[:, :qk].reshape(n, G, d), u[:, qk:2 * qk].reshape(n, G, d),
+                                           u[:, 2 * qk:].reshape(n, H, e), ba[:, :H], ba[:, H:], a_log, dt_bias)
+    state = torch.zeros(4, H * d * e, device=DEV)
+
+    def step(batch):                                   # [(slot, first, count)]
+        rows = sum(c for _, _, c in batch)
+        u = torch.cat([_t(seqs[s][0][f:f + c]) for s, f, c in batch if c] or [torch.zeros(0, 2 * qk + inner, device=DEV)])
+        proj = torch.cat([_t(seqs[s][1][f:f + c]) for s, f, c in batch if c])
+        starts = np.cumsum([0] + [c for _, _, c in batch])
+        o = torch.zeros(rows, inner, device=DEV)
+        ops.delta_rule(u, 0, qk, 2 * qk, proj, 0, H, _t(a_log), _t(dt_bias), state, _ints(starts), _ints([s for s, _, _ in batch]),
+                       o, len(batch), H, G, d, e)
+        for (s, f, c), r0 in zip(batch, starts):
+            _close(_np(o[r0:r0 + c]), want[s][f:f + c].reshape(c, inner), 3e-5, f"slot {s}, tokens {f}..{f + c - 1}")
+
+    step([(s, 0, prompt) for s in (3, 0, 2)])
+    for t in range(prompt, 10):
+        step([(s, t, 1) for s in (2, 3, 0)])
+    step([(0, 10, 1), (3, 10, 0), (2, 10, 2)])         # three rows, three requests
+    step([(3, 10, 1), (0, 11, 1)])
+    assert (state[1] == 0).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,e", [(4, 24), (3, 8), (2, 64), (5, 12), (1, 100)])
 def test_head_norm_with_gate(dtype, H, e):
