@@ -70,10 +70,10 @@ rglru_gates_kernel(const T* __restrict__ u, const float* __restrict__ wa_t, cons
 // with, writing the outputs. A tile costs one trip to global memory (every load is issued before the first use) and
 // 2 SC_LEN + SC_SEGS dependent multiply-adds instead of SC_SEGS x SC_LEN. Places past the request's end are the step
 // (1, 0), which changes nothing.
-constexpr int SC_SEGS = 8;
+// A step of single tokens runs one run a block (SC_SEGS = 1): 32 threads, a channel each.
 constexpr int SC_LEN = 16;
 
-template <typename T>
+template <typename T, int SC_SEGS>
 __global__ void __launch_bounds__(32 * SC_SEGS)
 rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ m, const T* __restrict__ y,
                   int y_stride, int y_col, const float* __restrict__ y_bias, float* __restrict__ state,
@@ -165,13 +165,18 @@ DL_EXPORT int dl_rglru_gates(int dtype, const void* u, const float* wa_t, const 
 // state_stride floats with S at their head; out: contiguous [rows, width].
 DL_EXPORT int dl_rglru_scan(int dtype, const float* a, const float* m, const void* y, int y_stride, int y_col,
                             const float* y_bias, float* state, long long state_stride, const int* q_start,
-                            const int* state_slots, void* out, int requests, int width, cudaStream_t stream) {
+                            const int* state_slots, void* out, int requests, int width, int rows, cudaStream_t stream) {
   if (requests <= 0 || width <= 0) return 0;
   if (requests > 65535) return DL_ERR_UNSUPPORTED;
-  const dim3 threads(32, dl::SC_SEGS);
   dim3 grid((width + 31) / 32, requests);
-  if (dtype == 0) dl::rglru_scan_kernel<float><<<grid, threads, 0, stream>>>(a, m, static_cast<const float*>(y), y_stride, y_col, y_bias, state, static_cast<size_t>(state_stride), q_start, state_slots, static_cast<float*>(out), width);
-  else if (dtype == 1) dl::rglru_scan_kernel<dl::bf16><<<grid, threads, 0, stream>>>(a, m, static_cast<const dl::bf16*>(y), y_stride, y_col, y_bias, state, static_cast<size_t>(state_stride), q_start, state_slots, static_cast<dl::bf16*>(out), width);
+#define DL_SCAN(T, SEGS)                                                                                                \
+  dl::rglru_scan_kernel<T, SEGS><<<grid, dim3(32, SEGS), 0, stream>>>(a, m, static_cast<const T*>(y), y_stride, y_col,  \
+                                                                      y_bias, state, static_cast<size_t>(state_stride), \
+                                                                      q_start, state_slots, static_cast<T*>(out), width)
+  const bool single = rows <= requests;         // no request brought more than a token or two
+  if (dtype == 0) { if (single) DL_SCAN(float, 1); else DL_SCAN(float, 16); }
+  else if (dtype == 1) { if (single) DL_SCAN(dl::bf16, 1); else DL_SCAN(dl::bf16, 16); }
   else return DL_ERR_UNSUPPORTED;
+#undef DL_SCAN
   return dl::launch_status();
 }

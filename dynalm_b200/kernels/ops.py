@@ -74,7 +74,7 @@ _SIGNATURES = {
         "dl_head_norm_gate": [_I, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _P]},
     "rglru": {
         "dl_rglru_gates": [_I, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
-        "dl_rglru_scan": [_I, _P, _P, _P, _I, _I, _P, _P, _L, _P, _P, _P, _I, _I, _P]},
+        "dl_rglru_scan": [_I, _P, _P, _P, _I, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _P]},
     "qk_proj_norm": {
         "dl_qk_proj_norm_cache": [_I, _P, _I, _P, _P, _F, _I, _P, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I,
                                   _I, _I, _P]},
@@ -1728,7 +1728,7 @@ def rglru_scan(a: torch.Tensor, m: torch.Tensor, y: torch.Tensor, y_col: int, y_
     _state_rows(state, width, "rglru_scan")
     check_limits("rglru", requests=state.shape[0], rows=rows)
     _check(_fn("rglru", "dl_rglru_scan")(dtype_code(y.dtype), _p(a), _p(m), _p(y), y.stride(0), y_col, _p(y_bias), _p(state),
-                                          state.stride(0), _p(q_start), _p(state_slots), _p(out), requests, width,
+                                          state.stride(0), _p(q_start), _p(state_slots), _p(out), requests, width, rows,
                                           _stream()), "rglru_scan")
 
 
