@@ -23,7 +23,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
                                int max_blocks, const int* __restrict__ positions,
                                const int* __restrict__ row_request, T* __restrict__ out, int out_stride,
                                int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
-                               int window, int vdim, size_t k_row, size_t v_row) {
+                               int window, int vdim, size_t k_row, size_t v_row, int wide) {
   __shared__ float red[33];
   __shared__ float sq[256];                 // the query, fp32
   __shared__ float sp[ATT_CHUNK];           // scores, then probabilities, of one chunk
@@ -51,13 +51,18 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
       float s = -INFINITY;
       if (t >= lo) {
         const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
-        const Vec16* kr = reinterpret_cast<const Vec16*>(k_cache + slot * k_row + static_cast<size_t>(kvh) * head_dim);
+        const T* kp = k_cache + slot * k_row + static_cast<size_t>(kvh) * head_dim;
         float dot = 0.0f;
-        for (int i = 0; i < head_dim / V; ++i) {
-          float f[V];
-          unpack<T>(kr[i], f);
+        if (wide) {                                     // every key starts on a 16-byte boundary
+          const Vec16* kr = reinterpret_cast<const Vec16*>(kp);
+          for (int i = 0; i < head_dim / V; ++i) {
+            float f[V];
+            unpack<T>(kr[i], f);
 #pragma unroll
-          for (int j = 0; j < V; ++j) dot = fmaf(sq[i * V + j], f[j], dot);
+            for (int j = 0; j < V; ++j) dot = fmaf(sq[i * V + j], f[j], dot);
+          }
+        } else {                                        // the same sum in the same order, number by number
+          for (int i = 0; i < head_dim; ++i) dot = fmaf(sq[i], to_float(kp[i]), dot);
         }
         s = dot * scale;
       }
@@ -105,24 +110,25 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
 // q: rows of `q_stride` elements with head h at column h * head_dim; out: rows of out_stride elements with head h at
 // column h * vdim. Keys of a token lie k_row elements apart from the next token's in k_cache (KV head j at j * head_dim),
 // values v_row elements apart in v_cache (KV head j at j * vdim): two arrays [pages, page_size, n_kv_heads, size], or
-// one array of records [k | v] given twice with two offsets. head_dim: a multiple of 16 up to 256 (bfloat16: every
-// key 16-byte aligned); vdim: 1 to 256.
+// one array of records [k | v] given twice with two offsets. head_dim and vdim: 1 to 256; keys that all start on a
+// 16-byte boundary are read 16 bytes at a time.
 DL_EXPORT int dl_paged_attention_generic_kv(int dtype, const void* q, int q_stride, const void* k_cache, long long k_row,
                                             const void* v_cache, long long v_row, const int* block_table, int max_blocks,
                                             const int* positions, const int* row_request, void* out, int out_stride,
                                             int rows, int n_heads, int n_kv_heads, int head_dim, int vdim, int page_size,
                                             float scale, int window, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (head_dim % 16 != 0 || head_dim > 256 || head_dim <= 0 || vdim <= 0 || vdim > 256 || n_kv_heads <= 0 ||
-      n_heads % n_kv_heads != 0 || page_size <= 0 || n_heads > 65535 || k_row % (dtype == 0 ? 4 : 8) != 0 ||
-      (reinterpret_cast<uintptr_t>(k_cache) & 15) != 0)
+  if (head_dim > 256 || head_dim <= 0 || vdim <= 0 || vdim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
+      page_size <= 0 || n_heads > 65535 || (dtype != 0 && dtype != 1))
     return DL_ERR_UNSUPPORTED;
+  const int per = dtype == 0 ? 4 : 8;           // numbers in 16 bytes
+  const int wide = head_dim % per == 0 && k_row % per == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
   dim3 grid(rows, n_heads);
 #define DL_LAUNCH(T)                                                                                          \
   dl::paged_attention_generic_kernel<T><<<grid, dl::ATT_THREADS, 0, stream>>>(                                 \
       static_cast<const T*>(q), q_stride, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, positions, row_request, static_cast<T*>(out), out_stride, n_heads, n_kv_heads, \
-      head_dim, page_size, scale, window, vdim, static_cast<size_t>(k_row), static_cast<size_t>(v_row))
+      head_dim, page_size, scale, window, vdim, static_cast<size_t>(k_row), static_cast<size_t>(v_row), wide)
   if (dtype == 0) DL_LAUNCH(float);
   else if (dtype == 1) DL_LAUNCH(dl::bf16);
   else return DL_ERR_UNSUPPORTED;

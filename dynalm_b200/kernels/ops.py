@@ -1767,8 +1767,8 @@ def paged_attention_generic_kv(q: torch.Tensor, k_cache: torch.Tensor, k_row: in
     _cuda(q, k_cache, v_cache, block_table, positions, row_request, out)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
-    if head_dim % 16 or head_dim > 256 or not 0 < vdim <= 256:
-        raise Unsupported(f"attention: keys of {head_dim} (a multiple of 16, at most 256) and values of {vdim} (at most 256)")
+    if not 0 < head_dim <= 256 or not 0 < vdim <= 256:
+        raise Unsupported(f"attention: keys of {head_dim} and values of {vdim} numbers (at most 256 each)")
     if n_heads % n_kv_heads:
         raise Unsupported(f"attention: {n_heads} heads do not divide into {n_kv_heads} KV heads")
     if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:

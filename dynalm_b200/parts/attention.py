@@ -183,9 +183,8 @@ class GatedNormedAttention(PagedAttention):
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
-        if spec.head_dim % 16 or not 0 < spec.head_dim <= 256 or not 0 < spec.value_dim <= 256:
-            raise Unsupported(f"gated_attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256, and "
-                              f"value_dim {spec.value_dim} at most 256")
+        if not 0 < spec.head_dim <= 256 or not 0 < spec.value_dim <= 256:
+            raise Unsupported(f"gated_attention: head_dim {spec.head_dim} and value_dim {spec.value_dim} must be at most 256")
         if spec.num_heads % spec.num_kv_heads:
             raise Unsupported(f"gated_attention: {spec.num_heads} heads do not divide into {spec.num_kv_heads} KV heads")
         if spec.get("qk_norm", "none") not in ("projection", "none"):

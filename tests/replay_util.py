@@ -206,9 +206,12 @@ def compare(plan: Plan, got: Dict[int, np.ndarray], plain: Dict[str, np.ndarray]
             what: str, spread: bool = False) -> float:
     """Every written row against the plain logits of its (request, position). Names the first bad
     row: its request, position and step. With `spread`, a row's error is the root mean square of the difference
-    (its mean taken off) over that of the plain logits (theirs taken off), and tol_rel bounds it alone: the measure
-    for 16-bit runs, where a single logit of a row can be several roundings off."""
+    (its mean taken off) over that of the plain logits (theirs taken off); tol_rel bounds every row and tol_abs the
+    median over all rows: the measure for 16-bit runs, where rounding has a long tail over the rows of a model with
+    random weights (five times the median at one row in a few hundred), while a fault of the cache, a window or a
+    state moves a row by its whole spread."""
     worst = 0.0
+    seen = []
     assert set(got) == set(plan.rows), f"{what}: steps with output {sorted(got)} != expected {sorted(plan.rows)}"
     for step in sorted(plan.rows):
         rows = plan.rows[step]
@@ -225,4 +228,7 @@ def compare(plan: Plan, got: Dict[int, np.ndarray], plain: Dict[str, np.ndarray]
             assert err <= bound, (f"{what}: first wrong row is step {step}, request {r}, position {pos}: "
                                   f"{'relative spread of the difference' if spread else 'max |diff|'} {err:.3g} > {bound:.3g}")
             worst = max(worst, err)
+            seen.append(err)
+    if spread and seen:
+        assert float(np.median(seen)) <= tol_abs, f"{what}: the median row is {float(np.median(seen)):.3g} > {tol_abs:.3g} off"
     return worst

@@ -47,12 +47,12 @@ O_A = {"architecture": "Rodelorn", "vocab": 300, "width": 96, "norm": {"eps": 1e
 
 # Sizes that defeat every vector path (a width that is no multiple of 8, an odd vocabulary), a delta layer first with
 # one query/key head for five heads and a single tap (nothing of the convolution is kept), attention without a window
-# and without a rotation whose keys and values have one size, one block of gate matrices, a window shorter than a
+# and without a rotation whose keys and values have one size that is no multiple of 16, one block of gate matrices, a window shorter than a
 # page with a rotation that is no multiple of four numbers, a layer without a feed-forward, no embedding scale, no
 # scale and no cap of the logits, no scales of the sides.
 O_B = {"architecture": "Rodelorn", "vocab": 257, "width": 100, "norm": {"eps": 3e-5}, "layers": [
     layer("delta", delta(5, 1, 20, 12, 1), 172),
-    layer("parallel", pair(attention(3, 3, 16, 16, 0.4), recurrence(40, 1, 2)), None),
+    layer("parallel", pair(attention(3, 3, 24, 24, 0.4), recurrence(40, 1, 2)), None),
     layer("parallel_2", pair(attention(6, 2, 16, 16, 0.3, window=7, dims=6, base=500.0), recurrence(36, 4, 1)), 172),
 ]}
 
@@ -64,7 +64,7 @@ O_C = {"architecture": "Rodelorn", "vocab": 272, "width": 128, "norm": {"eps": 1
            layer("delta", delta(2, 2, 128, 64, 4), 96),
            layer("parallel", pair(attention(4, 1, 64, 64, 0.11, window=64, dims=64, base=1e6), recurrence(96, 4, 5),
                                   1.0, 0.25), 96),
-           layer("parallel", pair(attention(2, 2, 16, 48, 0.5, window=33, dims=16, factor=2.0), recurrence(64, 2, 2),
+           layer("parallel", pair(attention(2, 2, 40, 48, 0.5, window=33, dims=16, factor=2.0), recurrence(64, 2, 2),
                                   2.0, 1.0), None),
            layer("delta_3", delta(4, 1, 40, 40, 5), 96),
        ]}

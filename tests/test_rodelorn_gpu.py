@@ -19,8 +19,9 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 # float32: (absolute, relative to the row's largest logit) on every logit. bfloat16: the spread of a row's difference
-# against the spread of its logits; rounding alone gives 0.015 to 0.02 in the middle and 0.08 at the worst row here.
-TOL = {"float32": (2e-5, 2e-5), "bfloat16": (0.0, 0.12)}
+# against the spread of its logits, (bound of the median row, bound of every row); rounding alone gives 0.015 to 0.02 at
+# the median row and up to 0.15 at the worst row of the worst-conditioned of the three models.
+TOL = {"float32": (2e-5, 2e-5), "bfloat16": (0.04, 0.3)}
 SPREAD = {"float32": False, "bfloat16": True}
 LENGTHS = {"oa": [5, 70, 150, 33, 260, 129], "ob": [1, 7, 64, 100, 129, 40], "oc": [3, 48, 95, 200, 16, 131]}
 SIZES = [16, 7, 2, 5, 3, 2, 11, 32, 2, 9, 64, 2]
@@ -359,7 +360,8 @@ def _records(cache, pages, page, n):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,e,rot,base,factor,normed", [(4, 2, 32, 16, 8, 1e4, 4.0, True), (6, 2, 16, 16, 6, 500.0, 1.0, True),
                                                             (3, 3, 16, 16, 0, 1.0, 1.0, True), (4, 1, 64, 64, 64, 1e6, 1.0, True),
-                                                            (2, 2, 16, 48, 16, 1e4, 2.0, False), (1, 1, 48, 8, 2, 7.0, 3.0, True)])
+                                                            (2, 2, 16, 48, 16, 1e4, 2.0, False), (1, 1, 48, 8, 2, 7.0, 3.0, True),
+                                                            (3, 1, 24, 24, 10, 1e4, 1.0, True), (2, 2, 7, 5, 6, 100.0, 1.0, True)])
 def test_whole_projection_norm_rotation_and_records(dtype, H, G, d, e, rot, base, factor, normed):
     """One statistic over all of q and one over all of k (heads of very unequal size, so that a statistic per head
     shows), plain weights, the first `rot` numbers of every head turned in pairs (i, i + rot / 2) by position over
@@ -395,7 +397,8 @@ def test_whole_projection_norm_rotation_and_records(dtype, H, G, d, e, rot, base
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,e,window", [(4, 2, 32, 16, 20), (6, 2, 16, 16, 7), (3, 3, 16, 16, 0), (4, 1, 64, 64, 64),
-                                            (2, 2, 16, 48, 33), (2, 1, 48, 8, 1), (8, 2, 128, 128, 130)])
+                                            (2, 2, 16, 48, 33), (2, 1, 48, 8, 1), (8, 2, 128, 128, 130), (3, 1, 24, 24, 9),
+                                            (2, 2, 40, 20, 0), (2, 1, 7, 5, 4)])
 def test_windowed_attention_with_a_key_made_to_stand_out(dtype, H, G, d, e, window):
     """Every query gets one key at a distance of its own whose score is made to stand out: the newest key, the oldest
     key that the window still holds, the one just outside it (which must NOT be seen), a page's last and first
