@@ -70,3 +70,19 @@ O_C = {"architecture": "Rodelorn", "vocab": 272, "width": 128, "norm": {"eps": 1
        ]}
 
 RODELORN = {"oa": (O_A, 61), "ob": (O_B, 62), "oc": (O_C, 63)}
+
+# Models of one kind of layer. Delta layers alone keep no pages at all (six taps, values wider than keys in one layer);
+# pairs alone keep no state rows of their own (five heads with five key/value heads of 72 numbers of which 36 turn,
+# values of 40, a window of three tokens in the second pair, seven taps, no embedding scale and no cap).
+_PB = pair(attention(5, 5, 72, 40, 0.2, window=70, dims=36, factor=3.0), recurrence(200, 5, 6), 0.3, 1.7)
+ONE_KIND = {
+    "only_delta": ({"architecture": "Rodelorn", "vocab": 301, "width": 72, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5},
+                    "logit_softcap": 5.0, "layers": [
+                        layer("delta", delta(6, 3, 48, 20, 6), 100),
+                        layer("delta_2", delta(2, 1, 24, 56, 2), None),
+                        layer("delta", delta(6, 3, 48, 20, 6), 100)]}, 64),
+    "only_pairs": ({"architecture": "Rodelorn", "vocab": 333, "width": 120, "norm": {"eps": 1e-5}, "logit_scale": 0.7, "layers": [
+        layer("parallel", _PB, 64),
+        layer("parallel_2", pair(attention(2, 1, 8, 8, 0.6, window=3, dims=2), recurrence(24, 3, 7)), 64),
+        layer("parallel", _PB, None)]}, 65),
+}

@@ -13,7 +13,7 @@ import torch
 import plain_rodelorn as plain
 from replay_util import (ROOT, compare, plan_chunks, plan_many_rows, plan_mixed, plan_tail, plan_whole, random_requests,
                          run_plan_in_process, run_plan_trace_run)
-from rodelorn_configs import RODELORN
+from rodelorn_configs import ONE_KIND, RODELORN
 
 pytestmark = pytest.mark.gpu
 
@@ -571,6 +571,23 @@ def test_many_single_token_rows_beside_a_portion(dtype, folders):
     built = _built(folders[dtype][name], dtype, need, 256, max_requests=24)
     got = run_plan_in_process(built.step_fn, plan)
     compare(plan, got, logits, *TOL[dtype], f"{name}/{dtype}/many rows", spread=SPREAD[dtype])
+
+
+@pytest.mark.parametrize("name", sorted(ONE_KIND))
+def test_models_of_one_kind_of_layer(name, tmp_path):
+    """Delta layers alone (no pages in the cache manager) and pairs alone, whole prompts and a mixed schedule, float32."""
+    from dynalm_b200.weights import write_model_folder
+    cfg, seed = ONE_KIND[name]
+    write_model_folder(str(tmp_path), cfg, seed, dtype=torch.float32)
+    reqs = random_requests(cfg["vocab"], [5, 300, 77, 130, 64], seed=3)
+    model = plain.PlainRodelorn(str(tmp_path))
+    logits = {r: model.logits(t) for r, t in reqs.items()}
+    for what, plan in (("whole", plan_whole(reqs)), ("mixed", plan_mixed(reqs, seed=4))):
+        need = plan.max_live_tokens(64)
+        built = _built(str(tmp_path), "float32", need, max(need, 64), max_requests=4)
+        got = run_plan_in_process(built.step_fn, plan)
+        compare(plan, got, logits, *TOL["float32"], f"{name}/{what}")
+        assert built.cache.free_pages == built.cache.num_pages
 
 
 @pytest.mark.parametrize("name", ["oa", "oc"])
