@@ -34,7 +34,7 @@ def _frozen(value: Any) -> Any:
 class Spec:
     """kind, width, named parameters, file tensors (local name -> name in the model file)."""
 
-    registry = ""          # which registry of dynalm_b200.parts builds it: "mixer", "feed_forward", "norm", "position"
+    registry = ""          # which registry of dynalm_b200.parts builds it: "mixer", "feed_forward", "norm", "position", "connection"
     __slots__ = ("kind", "width", "params", "tensors", "_key")
 
     def __init__(self, kind: str, width: int = 0, tensors: Optional[Mapping[str, str]] = None, **params: Any):
@@ -107,6 +107,15 @@ class FeedForwardSpec(Spec):
     """kind "gated_mlp" (parameters inner, activation): down(act(gate(x)) * up(x))."""
 
     registry = "feed_forward"
+    __slots__ = ()
+
+
+class ConnectionSpec(Spec):
+    """How a sublayer sits on the residual stream when that is more than one running sum. kind "hyper" (parameter
+    streams = n, tensors in [n], out [n], mix [n, n]): the sublayer reads sum_s in[s] x_s and every stream becomes
+    x_t <- sum_s mix[s, t] x_s + out[t] * result."""
+
+    registry = "connection"
     __slots__ = ()
 
 

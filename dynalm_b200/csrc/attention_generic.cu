@@ -1,8 +1,8 @@
 // Paged causal attention, one thread block per (query row, head): the plain kernel.
 //
 // It serves the true 32-bit path and every shape the faster kernels refuse. A row at position
-// `pos` of request r reads keys t in [lo, pos], lo = window > 0 ? max(0, pos - window + 1) : 0,
-// through block_table[r]; query head h reads KV head h / (heads / kv_heads).
+// `pos` of request r reads keys t in [lo, pos], lo = window > 0 ? max(0, pos - window + 1) : 0, and the keys
+// t < keep_first behind them, through block_table[r]; with `sink` the softmax's denominator holds one more term exp(0); query head h reads KV head h / (heads / kv_heads).
 //   s_t = scale * q.k_t;  out = sum_t exp(s_t - max) v_t / sum_t exp(s_t - max)
 // (dynacore/cpu/cpu_device.cpp:1309-1412,1717-1776). Keys are visited in chunks whose boundaries
 // are multiples of CHUNK in absolute position, merged by the running (max, sum, acc) rule of the
@@ -23,7 +23,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
                                int max_blocks, const int* __restrict__ positions,
                                const int* __restrict__ row_request, T* __restrict__ out, int out_stride,
                                int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
-                               int window, int vdim, size_t k_row, size_t v_row, int wide) {
+                               int window, int vdim, size_t k_row, size_t v_row, int wide, int keep_first,
+                               int sink) {
   __shared__ float red[33];
   __shared__ float sq[256];                 // the query, fp32
   __shared__ float sp[ATT_CHUNK];           // scores, then probabilities, of one chunk
@@ -44,12 +45,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
   const int g = tid / vdim, d = tid % vdim;           // valid when g < groups
 
   float m_run = -INFINITY, l_run = 0.0f, acc = 0.0f;  // acc: dim `tid` of the output, threads < head_dim
-  for (int c0 = (lo / ATT_CHUNK) * ATT_CHUNK; c0 <= pos; c0 += ATT_CHUNK) {
+  // keys below `keep_first` stay visible behind the window; chunks that hold no visible key are passed over
+  const int kept = lo > 0 ? min(keep_first, lo) : 0;
+  for (int c0 = kept > 0 ? 0 : (lo / ATT_CHUNK) * ATT_CHUNK; c0 <= pos; c0 += ATT_CHUNK) {
+    if (c0 + ATT_CHUNK <= lo && c0 >= kept) continue;
     const int c1 = min(c0 + ATT_CHUNK, pos + 1);
     float m_loc = -INFINITY;
     for (int t = c0 + tid; t < c1; t += ATT_THREADS) {
       float s = -INFINITY;
-      if (t >= lo) {
+      if (t >= lo || t < kept) {
         const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
         const T* kp = k_cache + slot * k_row + static_cast<size_t>(kvh) * head_dim;
         float dot = 0.0f;
@@ -84,8 +88,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
 
     float pv = 0.0f;
     if (g < groups) {
-      const int t0 = max(c0, lo);
-      for (int t = t0 + g; t < c1; t += groups) {
+      for (int t = c0 + g; t < c1; t += groups) {
+        if (t < lo && t >= kept) continue;
         const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
         pv = fmaf(sp[t - c0], to_float(v_cache[slot * v_row + static_cast<size_t>(kvh) * vdim + d]), pv);
       }
@@ -98,6 +102,12 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
       acc = acc * corr + sum;
     }
     __syncthreads();
+  }
+  if (sink) {                                            // one more term of score 0 in the denominator; it carries no value
+    const float m_fin = fmaxf(m_run, 0.0f);
+    const float corr = expf(m_run - m_fin);
+    l_run = l_run * corr + expf(-m_fin);
+    acc *= corr;
   }
   if (tid < vdim) {
     T* orow = out + static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * vdim;
@@ -112,14 +122,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
 // values v_row elements apart in v_cache (KV head j at j * vdim): two arrays [pages, page_size, n_kv_heads, size], or
 // one array of records [k | v] given twice with two offsets. head_dim and vdim: 1 to 256; keys that all start on a
 // 16-byte boundary are read 16 bytes at a time.
-DL_EXPORT int dl_paged_attention_generic_kv(int dtype, const void* q, int q_stride, const void* k_cache, long long k_row,
-                                            const void* v_cache, long long v_row, const int* block_table, int max_blocks,
-                                            const int* positions, const int* row_request, void* out, int out_stride,
-                                            int rows, int n_heads, int n_kv_heads, int head_dim, int vdim, int page_size,
-                                            float scale, int window, cudaStream_t stream) {
+DL_EXPORT int dl_paged_attention_generic_masked(int dtype, const void* q, int q_stride, const void* k_cache, long long k_row,
+                                                const void* v_cache, long long v_row, const int* block_table, int max_blocks,
+                                                const int* positions, const int* row_request, void* out, int out_stride,
+                                                int rows, int n_heads, int n_kv_heads, int head_dim, int vdim, int page_size,
+                                                float scale, int window, int keep_first, int sink, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (head_dim > 256 || head_dim <= 0 || vdim <= 0 || vdim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
-      page_size <= 0 || n_heads > 65535 || (dtype != 0 && dtype != 1))
+      page_size <= 0 || n_heads > 65535 || (dtype != 0 && dtype != 1) || keep_first < 0)
     return DL_ERR_UNSUPPORTED;
   const int per = dtype == 0 ? 4 : 8;           // numbers in 16 bytes
   const int wide = head_dim % per == 0 && k_row % per == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
@@ -128,12 +138,24 @@ DL_EXPORT int dl_paged_attention_generic_kv(int dtype, const void* q, int q_stri
   dl::paged_attention_generic_kernel<T><<<grid, dl::ATT_THREADS, 0, stream>>>(                                 \
       static_cast<const T*>(q), q_stride, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, positions, row_request, static_cast<T*>(out), out_stride, n_heads, n_kv_heads, \
-      head_dim, page_size, scale, window, vdim, static_cast<size_t>(k_row), static_cast<size_t>(v_row), wide)
+      head_dim, page_size, scale, window, vdim, static_cast<size_t>(k_row), static_cast<size_t>(v_row), wide,    \
+      keep_first, sink)
   if (dtype == 0) DL_LAUNCH(float);
   else if (dtype == 1) DL_LAUNCH(dl::bf16);
   else return DL_ERR_UNSUPPORTED;
 #undef DL_LAUNCH
   return dl::launch_status();
+}
+
+// The same with a plain window and an ordinary softmax.
+DL_EXPORT int dl_paged_attention_generic_kv(int dtype, const void* q, int q_stride, const void* k_cache, long long k_row,
+                                            const void* v_cache, long long v_row, const int* block_table, int max_blocks,
+                                            const int* positions, const int* row_request, void* out, int out_stride,
+                                            int rows, int n_heads, int n_kv_heads, int head_dim, int vdim, int page_size,
+                                            float scale, int window, cudaStream_t stream) {
+  return dl_paged_attention_generic_masked(dtype, q, q_stride, k_cache, k_row, v_cache, v_row, block_table, max_blocks,
+                                           positions, row_request, out, out_stride, rows, n_heads, n_kv_heads, head_dim, vdim,
+                                           page_size, scale, window, 0, 0, stream);
 }
 
 // The same for keys and values of one size in two arrays [pages, page_size, n_kv_heads, head_dim].

@@ -1,0 +1,162 @@
+// Gated linear attention: a matrix state per head with a decay per key channel.
+//
+// Per token and head (key size d, value size e), all float32:
+//
+//   alpha_i = sigmoid(z_i)^(1 / tau) = exp(-softplus(-z_i) / tau)          (z: the decay's projection, float32)
+//   S <- diag(alpha) S + k v^T                                              (S: d x e, row i belongs to key channel i)
+//   o = S^T (q * q_scale)                                                   (read after the write)
+//
+// The columns of S are independent recurrences that share alpha, k and q, so the kernel deals columns over threads: a
+// block is (a slice of columns, head, request); a column lies over P neighbouring lanes, each keeping R = Dp / P rows of
+// it in registers (Dp: d rounded up to P * R, the rows past d idle). Tokens are walked in tiles of 16 whose q, k, alpha
+// and v wait in shared memory; the outputs of a tile are written together. Nothing between one token and the next
+// depends on a shuffle: the sum over a column's lanes only finishes o.
+//
+// A request's state row holds S of every head TRANSPOSED, [H, e, d], so that a lane's rows of a column are neighbours
+// in memory. Steps of single tokens and portions of prompts run the same kernel.
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int GLA_TILE = 16;
+
+template <typename T, int R>
+__global__ void __launch_bounds__(256)
+gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, const float* __restrict__ z,
+                int z_stride, float inv_tau, float q_scale, float* __restrict__ state, size_t state_stride,
+                const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ o, int H, int d,
+                int e, int P, int cols) {
+  extern __shared__ __align__(16) float sm[];
+  const int Dp = P * R;
+  float* s_q = sm;                                // [TILE][Dp]
+  float* s_k = s_q + GLA_TILE * Dp;
+  float* s_a = s_k + GLA_TILE * Dp;
+  float* s_v = s_a + GLA_TILE * Dp;               // [TILE][cols]
+  float* s_o = s_v + GLA_TILE * cols;             // [TILE][cols]
+  const int req = blockIdx.z, head = blockIdx.y, c0 = blockIdx.x * cols;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int p = tid % P, cl = tid / P;            // lane within the column, column within the slice
+  const int col = c0 + cl;
+  const bool live = cl < cols && col < e;
+  const int r0 = q_start[req], r1 = q_start[req + 1];
+  if (r1 <= r0) return;
+  float* srow = state + static_cast<size_t>(state_slots[req]) * state_stride + (static_cast<size_t>(head) * e + col) * d;
+
+  // rows of this lane: i = 4 * (p + P * (j / 4)) + j % 4, so that at a given j the lanes of a column read neighbours
+  float S[R];
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int i = 4 * (p + P * (j >> 2)) + (j & 3);
+    S[j] = (live && i < d) ? srow[i] : 0.0f;
+  }
+
+  for (int t0 = r0; t0 < r1; t0 += GLA_TILE) {
+    const int nt = min(GLA_TILE, r1 - t0);
+    __syncthreads();                              // the tile before has been read
+    for (int x = tid; x < nt * Dp; x += nthr) {
+      const int t = x / Dp, i = x % Dp;
+      float qv = 0.0f, kv = 0.0f, av = 0.0f;
+      if (i < d) {
+        const T* prow = proj + static_cast<size_t>(t0 + t) * stride;
+        qv = to_float(prow[q_col + head * d + i]) * q_scale;
+        kv = to_float(prow[k_col + head * d + i]);
+        const float zz = -z[static_cast<size_t>(t0 + t) * z_stride + head * d + i];
+        const float sp = zz > 20.0f ? zz : log1pf(expf(zz));          // softplus(-z) = -log sigmoid(z)
+        av = expf(-sp * inv_tau);
+      }
+      s_q[x] = qv;
+      s_k[x] = kv;
+      s_a[x] = av;
+    }
+    for (int x = tid; x < nt * cols; x += nthr) {
+      const int t = x / cols, c = x % cols;
+      s_v[x] = c0 + c < e ? to_float(proj[static_cast<size_t>(t0 + t) * stride + v_col + head * e + c0 + c]) : 0.0f;
+    }
+    __syncthreads();
+    {                                             // every lane walks the tile (the shuffles name the whole warp)
+      const int clr = cl < cols ? cl : cols - 1;
+      for (int t = 0; t < nt; ++t) {
+        const float v = s_v[t * cols + clr];
+        const float* qa = s_q + t * Dp;
+        const float* ka = s_k + t * Dp;
+        const float* aa = s_a + t * Dp;
+        float acc = 0.0f;
+#pragma unroll
+        for (int j4 = 0; j4 < R / 4; ++j4) {
+          const int i = 4 * (p + P * j4);
+          const float4 q4 = *reinterpret_cast<const float4*>(qa + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(ka + i);
+          const float4 a4 = *reinterpret_cast<const float4*>(aa + i);
+          float* s = S + 4 * j4;
+          s[0] = fmaf(a4.x, s[0], k4.x * v);
+          s[1] = fmaf(a4.y, s[1], k4.y * v);
+          s[2] = fmaf(a4.z, s[2], k4.z * v);
+          s[3] = fmaf(a4.w, s[3], k4.w * v);
+          acc = fmaf(s[0], q4.x, acc);
+          acc = fmaf(s[1], q4.y, acc);
+          acc = fmaf(s[2], q4.z, acc);
+          acc = fmaf(s[3], q4.w, acc);
+        }
+        for (int off = P >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (p == 0 && cl < cols) s_o[t * cols + cl] = acc;
+      }
+    }
+    __syncthreads();
+    for (int x = tid; x < nt * cols; x += nthr) {
+      const int t = x / cols, c = x % cols;
+      if (c0 + c < e) o[static_cast<size_t>(t0 + t) * H * e + head * e + c0 + c] = s_o[x];
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const int i = 4 * (p + P * (j >> 2)) + (j & 3);
+      if (i < d) srow[i] = S[j];
+    }
+  }
+}
+
+}  // namespace dl
+
+// proj: rows of `stride` elements holding q (H * d numbers from column q_col), k (from k_col) and v (H * e from v_col).
+// z: float32 rows of z_stride numbers, H * d of them used. state: float32, a request's row state_stride numbers from the
+// next, the first H * e * d of it S transposed. q_start: requests + 1 row numbers. o: float32 [rows, H * e].
+DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, int k_col, int v_col, const float* z,
+                          int z_stride, float tau, float q_scale, float* state, long long state_stride, const int* q_start,
+                          const int* state_slots, float* o, int requests, int H, int d, int e, int sm_count,
+                          cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (H <= 0 || d <= 0 || d > 512 || e <= 0 || !(tau > 0.0f) || H > 65535 || requests > 65535 || (dtype != 0 && dtype != 1))
+    return DL_ERR_UNSUPPORTED;
+  int P = 1;
+  while (P * 16 < d) P <<= 1;                      // lanes a column: the fewest that leave a lane at most 16 rows
+  const int R = ((d + P - 1) / P + 3) / 4 * 4;     // rows a lane, in fours
+  int cols = 256 / P;                              // columns a block of 256 threads takes
+  if (cols > e) cols = e;
+  // fewer columns a block while the grid leaves SMs idle (a block keeps at least a warp's worth of lanes busy)
+  while (cols > 1 && cols * P > 32 && static_cast<long long>((e + cols - 1) / cols) * H * requests < sm_count) cols = (cols + 1) / 2;
+  const int threads = ((cols * P + 31) / 32) * 32;
+  const int Dp = P * R;
+  const size_t smem = static_cast<size_t>(dl::GLA_TILE) * (3 * Dp + 2 * cols) * sizeof(float);
+  dim3 grid((e + cols - 1) / cols, H, requests);
+#define DL_GLA(T, RR)                                                                                                    \
+  do {                                                                                                                   \
+    cudaFuncSetAttribute(dl::gla_scan_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::gla_scan_kernel<T, RR><<<grid, threads, smem, stream>>>(static_cast<const T*>(proj), stride, q_col, k_col, v_col, z, \
+                                                                z_stride, 1.0f / tau, q_scale, state,                    \
+                                                                static_cast<size_t>(state_stride), q_start, state_slots, o, \
+                                                                H, d, e, P, cols);                                       \
+  } while (0)
+#define DL_GLA_R(T)              \
+  do {                           \
+    if (R == 4) DL_GLA(T, 4);    \
+    else if (R == 8) DL_GLA(T, 8); \
+    else if (R == 12) DL_GLA(T, 12); \
+    else DL_GLA(T, 16);          \
+  } while (0)
+  if (dtype == 0) DL_GLA_R(float);
+  else DL_GLA_R(dl::bf16);
+#undef DL_GLA_R
+#undef DL_GLA
+  return dl::launch_status();
+}

@@ -1,0 +1,344 @@
+// Mixture of experts: routing, the grouping of (token, expert) pairs by expert, the experts' products over those
+// groups, and the weighted sum of a token's experts.
+//
+//   dl_moe_route     scores = softmax(router logits) over all experts, float32. Experts form `groups` equal groups of
+//                    neighbours; a group's score is its largest score and only experts of the `keep` best groups can be
+//                    chosen. The `top` allowed experts with the largest scores are chosen (equal scores: the lower
+//                    index), their weights are their scores divided by their sum (+ 1e-20), times `scale`.
+//   dl_moe_group     a counting sort of the tokens' pairs by expert: where every pair stands in that order, which pair
+//                    stands at every place, and the list of row tiles (expert, first place, places) for the products.
+//   dl_moe_linear    C[place] = act(A[row of place] W_e^T) for every place of every tile, W_e the matrix of the tile's
+//                    expert: a plain tiled product with float32 accumulation in a fixed order of k (any dtype), and one on
+//                    the tensor cores for bfloat16 (mma.sync m16n8k16, float32 accumulation).
+//   dl_moe_combine   y[t] = sum_k weight[t, k] * C[place of pair (t, k)], float32, in the order of k.
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int MOE_MAX_EXPERTS = 256;
+constexpr int MOE_TM = 32;          // places a tile
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int stride, int tokens, int E, int top, int groups,
+                                 int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float s[MOE_MAX_EXPERTS];
+  const float* z = logits + static_cast<size_t>(t) * stride;
+  float m = -INFINITY;
+  for (int i = 0; i < E; ++i) m = fmaxf(m, z[i]);
+  float sum = 0.0f;
+  for (int i = 0; i < E; ++i) {
+    s[i] = expf(z[i] - m);
+    sum += s[i];
+  }
+  const float inv = 1.0f / sum;
+  for (int i = 0; i < E; ++i) s[i] *= inv;
+  const int per = E / groups;
+  unsigned long long allowed_lo[MOE_MAX_EXPERTS / 64];      // bit g: group g is kept (groups <= experts <= 256)
+  for (int w = 0; w < MOE_MAX_EXPERTS / 64; ++w) allowed_lo[w] = 0ull;
+  if (keep >= groups) {
+    for (int g = 0; g < groups; ++g) allowed_lo[g >> 6] |= 1ull << (g & 63);
+  } else {
+    for (int r = 0; r < keep; ++r) {
+      int best = -1;
+      float bs = -INFINITY;
+      for (int g = 0; g < groups; ++g) {
+        if (allowed_lo[g >> 6] >> (g & 63) & 1ull) continue;
+        float gs = -INFINITY;
+        for (int i = g * per; i < (g + 1) * per; ++i) gs = fmaxf(gs, s[i]);
+        if (gs > bs) { bs = gs; best = g; }
+      }
+      if (best >= 0) allowed_lo[best >> 6] |= 1ull << (best & 63);
+    }
+  }
+  float wsum = 0.0f;
+  int* my_ids = ids + static_cast<size_t>(t) * top;
+  float* my_w = weights + static_cast<size_t>(t) * top;
+  for (int r = 0; r < top; ++r) {
+    int best = -1;
+    float bs = -INFINITY;
+    for (int i = 0; i < E; ++i) {
+      const int g = i / per;
+      if (!(allowed_lo[g >> 6] >> (g & 63) & 1ull)) continue;
+      bool taken = false;
+      for (int q = 0; q < r; ++q) taken |= my_ids[q] == i;
+      if (!taken && s[i] > bs) { bs = s[i]; best = i; }
+    }
+    if (best < 0) best = 0;                                  // (scores that are not numbers: some expert all the same)
+    my_ids[r] = best;
+    my_w[r] = s[best];
+    wsum += s[best];
+  }
+  const float f = scale / (wsum + 1e-20f);
+  for (int r = 0; r < top; ++r) my_w[r] *= f;
+}
+
+// One block. pairs = tokens * top. Outputs: place_of[pair], pair_at[place], tiles[3 * i] = (expert, first place,
+// places) for i < n_tiles[0].
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ place_of, int* __restrict__ pair_at,
+                 int* __restrict__ tiles, int* __restrict__ n_tiles) {
+  __shared__ int count[MOE_MAX_EXPERTS], first[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS], tile0[MOE_MAX_EXPERTS + 1];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < E; i += blockDim.x) { count[i] = 0; cursor[i] = 0; }
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) atomicAdd(&count[min(max(ids[p], 0), E - 1)], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0, tl = 0;
+    for (int i = 0; i < E; ++i) {
+      first[i] = at;
+      tile0[i] = tl;
+      at += count[i];
+      tl += (count[i] + MOE_TM - 1) / MOE_TM;
+    }
+    first[E] = at;
+    tile0[E] = tl;
+    n_tiles[0] = tl;
+  }
+  __syncthreads();
+  // Places inside an expert's run are dealt in the order in which the threads arrive: a run's order changes no
+  // result (every place is a product of its own), only which places share a tile.
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int ex = min(max(ids[p], 0), E - 1);
+    const int place = first[ex] + atomicAdd(&cursor[ex], 1);
+    place_of[p] = place;
+    pair_at[place] = p;
+  }
+  for (int i = tid; i < E; i += blockDim.x) {
+    const int nt = (count[i] + MOE_TM - 1) / MOE_TM;
+    for (int j = 0; j < nt; ++j) {
+      int* tl = tiles + 3 * (tile0[i] + j);
+      tl[0] = i;
+      tl[1] = first[i] + j * MOE_TM;
+      tl[2] = min(MOE_TM, count[i] - j * MOE_TM);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) { v = fmaxf(v, 0.0f); v = v * v; }
+  return v;
+}
+
+// Plain tiled product: tile = 32 places x 64 features, 256 threads, 2 x 4 results a thread, k in steps of 16.
+// A row of place p: a[(rows_of ? rows_of[pair_at[p]] / div : p) * lda]; W of expert x: w + x * N * K, [N, K].
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+moe_linear_simt_kernel(const T* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
+                       const T* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
+                       const int* __restrict__ n_tiles, int act) {
+  constexpr int TN = 64, TK = 16;
+  __shared__ float As[TK][MOE_TM + 1], Bs[TK][TN + 1];
+  __shared__ int src[MOE_TM];
+  if (static_cast<int>(blockIdx.y) >= n_tiles[0]) return;
+  const int* tl = tiles + 3 * blockIdx.y;
+  const int ex = tl[0], p0 = tl[1], np = tl[2];
+  const int n0 = blockIdx.x * TN;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (tid < MOE_TM) src[tid] = tid < np ? (pair_at != nullptr ? pair_at[p0 + tid] / top_div : p0 + tid) : -1;
+  __syncthreads();
+  const T* wx = w + static_cast<size_t>(ex) * N * K;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += TK) {
+    for (int x = tid; x < MOE_TM * TK; x += 256) {
+      const int r = x / TK, k = x % TK;
+      As[k][r] = (src[r] >= 0 && k0 + k < K) ? to_float(a[static_cast<size_t>(src[r]) * lda + k0 + k]) : 0.0f;
+    }
+    for (int x = tid; x < TN * TK; x += 256) {
+      const int n = x / TK, k = x % TK;
+      Bs[k][n] = (n0 + n < N && k0 + k < K) ? to_float(wx[static_cast<size_t>(n0 + n) * K + k0 + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TK; ++k) {
+      const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = Bs[k][tx * 4 + j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i;
+    if (r >= np) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) c[static_cast<size_t>(p0 + r) * ldc + n] = from_float<TO>(apply_act<T>(acc[i][j], act));
+    }
+  }
+}
+
+// bfloat16 on the tensor cores: tile = 32 places x 128 features, 8 warps, warp w takes features 16 w .. 16 w + 15 of the
+// tile for all 32 places (two m16 x two n8 fragments), k in steps of 32 through shared memory (rows padded to 40
+// numbers, so that the fragment loads of a warp fall on different banks).
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+moe_linear_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
+                      const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
+                      const int* __restrict__ n_tiles, int act) {
+  constexpr int TN = 128, TK = 32, LD = TK + 8;
+  __shared__ __align__(16) bf16 As[2][MOE_TM][LD];
+  __shared__ __align__(16) bf16 Bs[2][TN][LD];
+  __shared__ int src[MOE_TM];
+  if (static_cast<int>(blockIdx.y) >= n_tiles[0]) return;
+  const int* tl = tiles + 3 * blockIdx.y;
+  const int ex = tl[0], p0 = tl[1], np = tl[2];
+  const int n0 = blockIdx.x * TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MOE_TM) src[tid] = tid < np ? (pair_at != nullptr ? pair_at[p0 + tid] / top_div : p0 + tid) : -1;
+  __syncthreads();
+  const bf16* wx = w + static_cast<size_t>(ex) * N * K;
+  float acc[2][2][4] = {};
+  // a stage: A 32 x 32 numbers = 128 pieces of 16 bytes (threads 0..127), B 128 x 32 = 512 pieces (2 a thread)
+  auto load = [&](int stage, int k0) {
+    if (tid < 128) {
+      const int r = tid >> 2, piece = tid & 3;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (src[r] >= 0) v = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(src[r]) * lda + k0 + piece * 8);
+      *reinterpret_cast<uint4*>(&As[stage][r][piece * 8]) = v;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int x = tid + 256 * i, n = x >> 2, piece = x & 3;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (n0 + n < N) v = *reinterpret_cast<const uint4*>(wx + static_cast<size_t>(n0 + n) * K + k0 + piece * 8);
+      *reinterpret_cast<uint4*>(&Bs[stage][n][piece * 8]) = v;
+    }
+  };
+  const int steps = K / TK;
+  load(0, 0);
+  __syncthreads();
+  const int g = lane >> 2, q = lane & 3;
+  for (int s = 0; s < steps; ++s) {
+    const int st = s & 1;
+    if (s + 1 < steps) load(st ^ 1, (s + 1) * TK);
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t af[2][4], bfr[2][2];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        const bf16* base = &As[st][mi * 16][0];
+        af[mi][0] = *reinterpret_cast<const uint32_t*>(base + g * LD + kk + q * 2);
+        af[mi][1] = *reinterpret_cast<const uint32_t*>(base + (g + 8) * LD + kk + q * 2);
+        af[mi][2] = *reinterpret_cast<const uint32_t*>(base + g * LD + kk + 8 + q * 2);
+        af[mi][3] = *reinterpret_cast<const uint32_t*>(base + (g + 8) * LD + kk + 8 + q * 2);
+      }
+#pragma unroll
+      for (int ni = 0; ni < 2; ++ni) {
+        const bf16* base = &Bs[st][warp * 16 + ni * 8 + g][0];
+        bfr[ni][0] = *reinterpret_cast<const uint32_t*>(base + kk + q * 2);
+        bfr[ni][1] = *reinterpret_cast<const uint32_t*>(base + kk + 8 + q * 2);
+      }
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni) mma_bf16_16816(acc[mi][ni], af[mi], bfr[ni]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = mi * 16 + g + 8 * h;
+        const int n = n0 + warp * 16 + ni * 8 + q * 2;
+        if (r >= np) continue;
+        TO* dst = c + static_cast<size_t>(p0 + r) * ldc + n;
+        if (n < N) dst[0] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h], act));
+        if (n + 1 < N) dst[1] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h + 1], act));
+      }
+}
+
+template <typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ c, int width, const int* __restrict__ place_of,
+                                   const float* __restrict__ weights, int top, TO* __restrict__ y, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / width;
+  const int col = static_cast<int>(i % width);
+  float sum = 0.0f;
+  for (int k = 0; k < top; ++k)
+    sum = fmaf(weights[t * top + k], c[static_cast<size_t>(place_of[t * top + k]) * width + col], sum);
+  y[i] = from_float<TO>(sum);
+}
+
+}  // namespace dl
+
+DL_EXPORT int dl_moe_route(const float* logits, int stride, int tokens, int E, int top, int groups, int keep, float scale,
+                           int* ids, float* weights, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (E <= 0 || E > dl::MOE_MAX_EXPERTS || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+      top > keep * (E / groups))
+    return DL_ERR_UNSUPPORTED;
+  dl::moe_route_kernel<<<(tokens + 127) / 128, 128, 0, stream>>>(logits, stride, tokens, E, top, groups, keep, scale, ids, weights);
+  return dl::launch_status();
+}
+
+DL_EXPORT int dl_moe_group(const int* ids, int pairs, int E, int* place_of, int* pair_at, int* tiles, int* n_tiles,
+                           cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (E <= 0 || E > dl::MOE_MAX_EXPERTS) return DL_ERR_UNSUPPORTED;
+  dl::moe_group_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, place_of, pair_at, tiles, n_tiles);
+  return dl::launch_status();
+}
+
+// dtype of a and w: 0 float32, 1 bfloat16; out_dtype of c likewise. pair_at null: the rows of a are the places
+// themselves; else the row of a place is pair_at[place] / top_div. act: 0 none, 1 squared ReLU. tensor_cores: use the
+// mma.sync kernel where it applies (bfloat16, K a multiple of 32, rows of a and w on 16-byte boundaries).
+DL_EXPORT int dl_moe_linear(int dtype, int out_dtype, const void* a, int lda, const int* pair_at, int top_div, const void* w,
+                            int N, int K, void* c, int ldc, const int* tiles, const int* n_tiles, int max_tiles, int act,
+                            int tensor_cores, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0 || top_div <= 0 || max_tiles > 65535) return DL_ERR_UNSUPPORTED;
+  if (dtype == 1 && tensor_cores && K % 32 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    dim3 grid((N + 127) / 128, max_tiles);
+    if (out_dtype == 1)
+      dl::moe_linear_mma_kernel<dl::bf16><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
+                                                                     static_cast<const dl::bf16*>(w), N, K,
+                                                                     static_cast<dl::bf16*>(c), ldc, tiles, n_tiles, act);
+    else if (out_dtype == 0)
+      dl::moe_linear_mma_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
+                                                                  static_cast<const dl::bf16*>(w), N, K, static_cast<float*>(c),
+                                                                  ldc, tiles, n_tiles, act);
+    else return DL_ERR_UNSUPPORTED;
+    return dl::launch_status();
+  }
+  dim3 grid((N + 63) / 64, max_tiles);
+#define DL_MOE(T, TO)                                                                                                      \
+  dl::moe_linear_simt_kernel<T, TO><<<grid, 256, 0, stream>>>(static_cast<const T*>(a), lda, pair_at, top_div,              \
+                                                              static_cast<const T*>(w), N, K, static_cast<TO*>(c), ldc, tiles, \
+                                                              n_tiles, act)
+  if (dtype == 0 && out_dtype == 0) DL_MOE(float, float);
+  else if (dtype == 1 && out_dtype == 1) DL_MOE(dl::bf16, dl::bf16);
+  else if (dtype == 1 && out_dtype == 0) DL_MOE(dl::bf16, float);
+  else return DL_ERR_UNSUPPORTED;
+#undef DL_MOE
+  return dl::launch_status();
+}
+
+DL_EXPORT int dl_moe_combine(int out_dtype, const float* c, int width, const int* place_of, const float* weights, int top,
+                             void* y, int tokens, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const size_t total = static_cast<size_t>(tokens) * width;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (out_dtype == 0) dl::moe_combine_kernel<float><<<blocks, 256, 0, stream>>>(c, width, place_of, weights, top, static_cast<float*>(y), total);
+  else if (out_dtype == 1) dl::moe_combine_kernel<dl::bf16><<<blocks, 256, 0, stream>>>(c, width, place_of, weights, top, static_cast<dl::bf16*>(y), total);
+  else return DL_ERR_UNSUPPORTED;
+  return dl::launch_status();
+}

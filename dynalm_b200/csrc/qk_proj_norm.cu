@@ -75,6 +75,81 @@ qk_proj_norm_kernel(T* __restrict__ proj, int stride, const float* __restrict__ 
   }
 }
 
+
+// The other order: turn first, then make every head of q and k a unit-RMS vector by itself (no weight), or leave it
+// as it is. One warp per unit, a unit being a query head, a key head or the values of a KV head. The pairs of the
+// rotation are (i, i + rot / 2) or, interleaved, (2i, 2i + 1); a pair (u, v) turns to (u cos a - v sin a, v cos a + u
+// sin a), a = position * inv_freq[i], in float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rot_head_norm_kernel(T* __restrict__ proj, int stride, const float* __restrict__ inv_freq, int rot, int interleaved,
+                        int unit_norm, float eps, const int* __restrict__ positions, const int* __restrict__ row_slot,
+                        const int* __restrict__ block_table, int max_blocks, T* __restrict__ k_cache, size_t k_row,
+                        T* __restrict__ v_cache, size_t v_row, int rows, int H, int G, int d, int e, int page_size) {
+  constexpr int PER = 8;                                   // numbers a lane holds: heads of up to 256
+  const int units = H + 2 * G;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= static_cast<long long>(rows) * units) return;
+  const int row = static_cast<int>(unit / units), u = static_cast<int>(unit % units);
+  const int pos = positions[row];
+  const int* table = block_table + static_cast<size_t>(ck_request(row_slot[row])) * max_blocks;
+  T* base = proj + static_cast<size_t>(row) * stride;
+  size_t slot = 0;
+  int page = 0;
+  if (u >= H) {
+    page = ck_page_store(table, pos / page_size, max_blocks);
+    slot = static_cast<size_t>(page < 0 ? 0 : page) * page_size + pos % page_size;
+  }
+  if (u >= H + G) {                                         // values: a copy into the token's place
+    if (page < 0) return;
+    const T* v = base + H * d + G * d + (u - H - G) * e;
+    T* dst = v_cache + slot * v_row + static_cast<size_t>(u - H - G) * e;
+    for (int i = lane; i < e; i += 32) dst[i] = v[i];
+    return;
+  }
+  T* src = base + (u < H ? u * d : H * d + (u - H) * d);
+  const int half = rot / 2;
+  float x[PER], xp[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    x[j] = i < d ? to_float(src[i]) : 0.0f;
+    xp[j] = 0.0f;
+    if (i < rot) {
+      const int partner = interleaved ? (i ^ 1) : (i < half ? i + half : i - half);
+      xp[j] = to_float(src[partner]);
+    }
+  }
+  __syncwarp();                                             // every lane has read before any lane writes in place
+  const float fpos = static_cast<float>(pos);
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    if (i < rot) {
+      const bool first = interleaved ? !(i & 1) : i < half;
+      const int f = interleaved ? (i >> 1) : (first ? i : i - half);
+      float sn, cs;
+      sincosf(fpos * inv_freq[f], &sn, &cs);
+      x[j] = first ? x[j] * cs - xp[j] * sn : x[j] * cs + xp[j] * sn;
+    }
+    ss = fmaf(x[j], x[j], ss);
+  }
+  float r = 1.0f;
+  if (unit_norm) r = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(d) + eps);
+  T* dst = src;
+  if (u >= H) {
+    if (page < 0) return;
+    dst = k_cache + slot * k_row + static_cast<size_t>(u - H) * d;
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    if (i < d) dst[i] = from_float<T>(x[j] * r);
+  }
+}
+
 }  // namespace dl
 
 DL_EXPORT int dl_qk_proj_norm_cache(int dtype, void* proj, int stride, const float* wq, const float* wk, float eps, int do_norm,
@@ -91,6 +166,33 @@ DL_EXPORT int dl_qk_proj_norm_cache(int dtype, void* proj, int stride, const flo
                                                        static_cast<T*>(k_cache), static_cast<size_t>(k_row),              \
                                                        static_cast<T*>(v_cache), static_cast<size_t>(v_row), H, G, d, e,  \
                                                        page_size)
+  if (dtype == 0) DL_QK(float);
+  else if (dtype == 1) DL_QK(dl::bf16);
+  else return DL_ERR_UNSUPPORTED;
+#undef DL_QK
+  return dl::launch_status();
+}
+
+// Rows [q: H*d | k: G*d | v: G*e | ...]: rotation first (rot numbers of every head, pairs by halves or interleaved),
+// then every head of q and k divided by its own root mean square (unit_norm) or left; q in place, k and v into the
+// pages. d at most 256.
+DL_EXPORT int dl_qk_rot_head_norm_cache(int dtype, void* proj, int stride, const float* inv_freq, int rot, int interleaved,
+                                        int unit_norm, float eps, const int* positions, const int* row_slot,
+                                        const int* block_table, int max_blocks, void* k_cache, long long k_row,
+                                        void* v_cache, long long v_row, int rows, int H, int G, int d, int e, int page_size,
+                                        cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || G <= 0 || d <= 0 || d > 256 || e <= 0 || rot < 0 || rot > d || (rot & 1) || page_size <= 0 ||
+      (rot > 0 && inv_freq == nullptr))
+    return DL_ERR_UNSUPPORTED;
+  const long long units = static_cast<long long>(rows) * (H + 2 * G);
+  const unsigned blocks = static_cast<unsigned>((units + 7) / 8);
+#define DL_QK(T)                                                                                                          \
+  dl::qk_rot_head_norm_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<T*>(proj), stride, inv_freq, rot, interleaved,   \
+                                                             unit_norm, eps, positions, row_slot, block_table, max_blocks, \
+                                                             static_cast<T*>(k_cache), static_cast<size_t>(k_row),         \
+                                                             static_cast<T*>(v_cache), static_cast<size_t>(v_row), rows, H, \
+                                                             G, d, e, page_size)
   if (dtype == 0) DL_QK(float);
   else if (dtype == 1) DL_QK(dl::bf16);
   else return DL_ERR_UNSUPPORTED;

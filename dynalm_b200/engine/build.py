@@ -56,7 +56,7 @@ def build(model_dir: Optional[str] = None, *, config_obj: Optional[Mapping[str, 
             raise InvalidArgument("build needs a model folder, or a configuration and its tensors")
         arch = find_architecture(config_obj)
         config = arch.read_config(config_obj)
-        plan = arch.plan(config, present=set(tensors))
+        plan = arch.plan(config, present={n: tuple(t.shape) for n, t in tensors.items()})
         check_tensors("tensors", plan, {n: tuple(t.shape) for n, t in tensors.items()})
         store = place_tensors(plan, tensors, runtime.device, compute)
     model = Decoder(plan, store, runtime)

@@ -74,9 +74,9 @@ class _Layout:
 
 
 class _Record:
-    __slots__ = ("calls", "own", "library", "pending", "pending_scale", "pending2", "as_input")
+    __slots__ = ("calls", "own", "library", "pending", "pending_scale", "pending2", "as_input", "streams", "parts")
 
-    def __init__(self, calls, pending, pending_scale, pending2=None, as_input=None):
+    def __init__(self, calls, pending, pending_scale, pending2=None, as_input=None, streams=None, parts=1):
         # [(function, arguments, ((argument index, tensor index, offset or None for the tensor itself), ...))]
         self.calls = calls
         self.library = sum(1 for f, _, _ in calls if f is ops.library_mm_again)
@@ -85,6 +85,8 @@ class _Record:
         self.pending_scale = pending_scale
         self.pending2 = pending2
         self.as_input = as_input
+        self.streams = streams
+        self.parts = parts
 
 
 def _patches(calls, layout: _Layout):
@@ -119,7 +121,7 @@ class LayerLaunchMemo:
         self.kinds = kinds                  # run-order entry -> a number that blocks of equal class and spec share
         self.records: Dict[tuple, Optional[_Record]] = {}
 
-    def _layout(self, index: int, block, cache) -> _Layout:
+    def _layout(self, index: int, block, cache, stream=None) -> _Layout:
         got = self.layouts.get(index)
         if got is None or got[0] is not cache:             # the view is kept, so that no other object can take its place
             tensors = owned_tensors(block)
@@ -127,6 +129,11 @@ class LayerLaunchMemo:
                 tensors = tensors + list(cache.arrays) + ([cache.block_table] if cache.block_table is not None else [])
                 if getattr(cache, "state", None) is not None:
                     tensors = tensors + list(cache.state.arrays)
+            # tensors of the layer in front that this layer's first launches read (the weights with which its last
+            # result enters a stream of several parts): they differ from layer to layer like the layer's own
+            entry = getattr(block, "entry_tensors", None)
+            if entry is not None and stream is not None:
+                tensors = tensors + list(entry(stream))
             got = (cache, _Layout(tensors))
             self.layouts[index] = got
         return got[1]
@@ -134,12 +141,14 @@ class LayerLaunchMemo:
     def run(self, index: int, block, stream, ctx, cache, owns_cache: bool):
         if not getattr(block, "replay_safe", False):
             return block.forward(stream, ctx, cache, owns_cache)
-        layout = self._layout(index, block, cache)
+        layout = self._layout(index, block, cache, stream)
         pending, second = stream.pending, stream.pending2
         key = (self.kinds[index], owns_cache, stream.x.data_ptr(), stream.pending_scale,
                None if pending is None else (pending.data_ptr(), tuple(pending.shape), pending.dtype),
                None if second is None else (second.data_ptr(), tuple(second.shape), second.dtype),
-               None if stream.as_input is None else stream.as_input.data_ptr(), layout.signature)
+               None if stream.as_input is None else stream.as_input.data_ptr(),
+               None if stream.streams is None else (stream.streams.data_ptr(), stream.parts, stream.link is not None),
+               layout.signature)
         if key in self.records:
             record = self.records[key]
             if record is None:
@@ -159,6 +168,9 @@ class LayerLaunchMemo:
             REPLAYED_LAYERS += 1
             stream.pending, stream.pending_scale, stream.pending2 = record.pending, record.pending_scale, record.pending2
             stream.as_input = record.as_input
+            if record.streams is not None:
+                # the pending result belongs to the last sublayer of THIS layer: its stream connection, not the recorded one
+                stream.streams, stream.parts, stream.link = record.streams, record.parts, block.last_link()
             return stream
         with ops.Recording() as recording:
             stream = block.forward(stream, ctx, cache, owns_cache)
@@ -166,5 +178,5 @@ class LayerLaunchMemo:
             self.records[key] = None             # some work was not written down: this kind runs through its parts
         else:
             self.records[key] = _Record(_patches(recording.calls, layout), stream.pending, stream.pending_scale,
-                                        stream.pending2, stream.as_input)
+                                        stream.pending2, stream.as_input, stream.streams, stream.parts)
         return stream

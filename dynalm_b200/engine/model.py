@@ -106,6 +106,13 @@ class Decoder:
 
     def _final_norm(self, stream: ResidualStream, normed: torch.Tensor, ctx) -> None:
         """The final norm of the wanted rows, with what the last block left pending added on the way in."""
+        if stream.streams is not None and hasattr(self.final_norm, "forward_stream"):
+            # a stream of several parts: the norm reads their plain sum, after the last sublayer's update
+            self.final_norm.forward_stream(stream.streams, stream.parts, normed, delta=stream.pending, link=stream.link,
+                                           rows=ctx.logit_rows)
+            return
+        if stream.streams is not None:
+            stream.flush()
         if stream.pending2 is not None and hasattr(self.final_norm, "forward_pair") and stream.pending_scale == 1.0:
             self.final_norm.forward_pair(stream.x, normed, None, None, delta_a=stream.pending, delta_b=stream.pending2,
                                          rows=ctx.logit_rows)

@@ -67,7 +67,9 @@ _SIGNATURES = {
     "attention_generic": {
         "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "dl_paged_attention_generic_kv": [_I, _P, _I, _P, _L, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
-                                          _P]},
+                                          _P],
+        "dl_paged_attention_generic_masked": [_I, _P, _I, _P, _L, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F,
+                                              _I, _I, _I, _P]},
     "delta_rule": {
         "dl_delta_rule": [_I, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "dl_delta_rule_step": [_I, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -77,7 +79,19 @@ _SIGNATURES = {
         "dl_rglru_scan": [_I, _P, _P, _P, _I, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _P]},
     "qk_proj_norm": {
         "dl_qk_proj_norm_cache": [_I, _P, _I, _P, _P, _F, _I, _P, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I,
-                                  _I, _I, _P]},
+                                  _I, _I, _P],
+        "dl_qk_rot_head_norm_cache": [_I, _P, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I,
+                                      _P]},
+    "layer_norm": {
+        "dl_stream_layer_norm": [_I, _I, _P, _I, _I, _P, _P, _I, _L, _F, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
+        "dl_stream_sum": [_I, _P, _I, _I, _P, _I, _L, _F, _P, _P, _P, _I, _P]},
+    "gla": {
+        "dl_gla_scan": [_I, _P, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P]},
+    "moe": {
+        "dl_moe_route": [_P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
+        "dl_moe_group": [_P, _I, _I, _P, _P, _P, _P, _P],
+        "dl_moe_linear": [_I, _I, _P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P],
+        "dl_moe_combine": [_I, _P, _I, _P, _P, _I, _P, _I, _P]},
     "gates": {
         "dl_gelu_mul": [_I, _P, _P, _I, _I, _P],
         "dl_sigmoid_gate": [_I, _P, _I, _P, _I, _I, _I, _P],
@@ -1760,10 +1774,11 @@ def qk_proj_norm_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optio
 def paged_attention_generic_kv(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int,
                                block_table: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,
                                out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, vdim: int, page_size: int,
-                               scale: float, window: int = 0) -> None:
+                               scale: float, window: int = 0, keep_first: int = 0, sink: bool = False) -> None:
     """paged_attention_generic with keys of head_dim and values of vdim numbers: k_cache / v_cache point at the first
     token's keys / values (KV head j at j * head_dim / j * vdim), k_row / v_row elements lie between two tokens.
-    out: rows with head h at column h * vdim."""
+    out: rows with head h at column h * vdim. keep_first: keys at positions below it stay visible behind the window;
+    sink: the softmax's denominator holds one more term of score 0, which carries no value."""
     _cuda(q, k_cache, v_cache, block_table, positions, row_request, out)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -1774,10 +1789,10 @@ def paged_attention_generic_kv(q: torch.Tensor, k_cache: torch.Tensor, k_row: in
     if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
         raise InvalidArgument("attention: q, out and the cache must share one dtype")
     check_limits("attention_generic", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
-    _check(_fn("attention_generic", "dl_paged_attention_generic_kv")(
+    _check(_fn("attention_generic", "dl_paged_attention_generic_masked")(
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table),
         block_table.stride(0), _p(positions), _p(row_request), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads,
-        head_dim, vdim, page_size, scale, window, _stream()), "paged_attention_generic_kv")
+        head_dim, vdim, page_size, scale, window, int(keep_first), 1 if sink else 0, _stream()), "paged_attention_generic_kv")
 
 
 def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -1840,3 +1855,182 @@ def norm_add_norm(x: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, ep
     _check(_fn("norm_sandwich", "dl_norm_add_norm")(od, dtype_code(delta.dtype), _p(x), _p(delta), parts, part_stride,
                                                      _p(w_post), eps_post, _p(w_pre), eps_pre, _p(out), rows, width,
                                                      _stream()), "norm_add_norm")
+
+
+def qk_rot_head_norm_cache(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, interleaved: bool, unit_norm: bool,
+                           eps: float, positions: torch.Tensor, row_slot: torch.Tensor, block_table: torch.Tensor,
+                           k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int, heads: int, kv_heads: int,
+                           dim: int, vdim: int, page_size: int) -> None:
+    """Rows [q: H*d | k: G*d | v: G*e | ...] of a projection: the first `rot` numbers of every head of q and k turned by
+    position (pairs i, i + rot/2, or 2i, 2i + 1 when interleaved), then every head divided by its own root mean square
+    (unit_norm) or left; q written back in place, k and v written to the token's place in the cache (k_cache / v_cache
+    point at the first token's keys / values, k_row / v_row elements lie between two tokens). See csrc/qk_proj_norm.cu."""
+    _cuda(proj, inv_freq, positions, row_slot, block_table, k_cache, v_cache)
+    _rows_contiguous(proj, "proj")
+    if proj.shape[1] < heads * dim + kv_heads * (dim + vdim) or k_cache.dtype != proj.dtype or v_cache.dtype != proj.dtype:
+        raise InvalidArgument("qk_rot_head_norm_cache: proj holds q | k | v; the cache has proj's dtype")
+    if dim > 256:
+        raise Unsupported(f"qk_rot_head_norm_cache: heads of {dim} numbers (256 at most)")
+    if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
+        raise InvalidArgument("qk_rot_head_norm_cache: inv_freq float32 [rot / 2]")
+    check_limits("qk_proj_norm", pages=k_cache.shape[0], requests=block_table.shape[0], rows=proj.shape[0])
+    _check(_fn("qk_proj_norm", "dl_qk_rot_head_norm_cache")(
+        dtype_code(proj.dtype), _p(proj), proj.stride(0), _p(inv_freq), rot, 1 if interleaved else 0, 1 if unit_norm else 0,
+        eps, _p(positions), _p(row_slot), _p(block_table), block_table.stride(0), _p(k_cache), k_row, _p(v_cache), v_row,
+        proj.shape[0], heads, kv_heads, dim, vdim, page_size, _stream()), "qk_rot_head_norm_cache")
+
+
+STREAM_MAX_PARTS = 8       # the most parts a residual stream may have (csrc/layer_norm.cu)
+
+
+def stream_layer_norm(streams: torch.Tensor, parts: int, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
+                      out: Optional[torch.Tensor], init: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
+                      delta_scale: float = 1.0, mix: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None,
+                      read: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                      n_rows: Optional[int] = None) -> None:
+    """Layer norm over a residual stream of `parts` parts, fused with the update the sublayer in front left pending.
+
+    streams: float32 [n, parts * width] (a row's parts one after the other), updated in place unless `rows` gathers.
+    init [n, width] float32: every part of a row starts as this row (the first layer). delta: the sublayer's result,
+    [n, width] of either dtype or [k, n, width] partial sums; then x_t <- sum_s mix[s, t] x_s + write[t] * delta_scale *
+    delta (mix float32 [parts, parts] or None = identity; write float32 [parts] or None = ones). The norm reads u =
+    sum_t read[t] x_t (None = ones): out[r] = (u - mean) / sqrt(var + eps) * weight + bias for row rows[r] or r. out None:
+    only the update is made."""
+    _cuda(streams, weight, bias, out, init, delta, mix, write, read, rows)
+    width = weight.numel()
+    if streams.dtype != torch.float32 or not streams.is_contiguous() or streams.shape[-1] != parts * width \
+            or weight.dtype != torch.float32 or not 0 < parts <= STREAM_MAX_PARTS:
+        raise InvalidArgument("stream_layer_norm: streams float32 contiguous [n, parts * width], weight float32 [width]")
+    for t, n in ((bias, width), (mix, parts * parts), (write, parts), (read, parts)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise InvalidArgument("stream_layer_norm: bias, mix, write and read are float32 of width, parts^2, parts, parts")
+    if init is not None and (init.dtype != torch.float32 or not init.is_contiguous() or init.shape[-1] != width):
+        raise InvalidArgument("stream_layer_norm: init float32 contiguous [n, width]")
+    total = streams.shape[0]
+    if out is not None:
+        if not out.is_contiguous() or out.shape[-1] != width:
+            raise InvalidArgument("stream_layer_norm: out contiguous [rows, width]")
+        n_out = out.shape[0]
+    else:
+        n_out = total if n_rows is None else n_rows
+    if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n_out):
+        raise InvalidArgument("stream_layer_norm: rows must be int32 with one entry per output row")
+    if rows is None and total < n_out:
+        raise InvalidArgument("stream_layer_norm: fewer input rows than output rows")
+    k, part_stride = _delta_parts(delta, width, "stream_layer_norm")
+    out_code = dtype_code(out.dtype) if out is not None else 0
+    dd = dtype_code(delta.dtype) if delta is not None else out_code
+    check_limits("layer_norm", rows=total)
+    _take_ahead()
+    _check(_fn("layer_norm", "dl_stream_layer_norm")(
+        out_code, dd, _p(streams), parts, width, _p(init), _p(delta), k, part_stride, delta_scale, _p(mix), _p(write),
+        _p(read), _p(weight), _p(bias), eps, _p(out), _p(rows), n_out, total, _stream()), "stream_layer_norm")
+
+
+def stream_sum(streams: torch.Tensor, parts: int, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+               delta_scale: float = 1.0, mix: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None) -> None:
+    """out[n, width] (float32) = the sum of a stream's parts, after the pending update of stream_layer_norm (which is
+    not written back)."""
+    _cuda(streams, out, delta, mix, write)
+    rows, width = out.shape
+    if streams.dtype != torch.float32 or out.dtype != torch.float32 or not streams.is_contiguous() or not out.is_contiguous() \
+            or streams.shape[-1] != parts * width or streams.shape[0] < rows:
+        raise InvalidArgument("stream_sum: streams float32 [n, parts * width], out float32 [n, width]")
+    k, part_stride = _delta_parts(delta, width, "stream_sum")
+    _check(_fn("layer_norm", "dl_stream_sum")(dtype_code(delta.dtype) if delta is not None else 0, _p(streams), parts, width,
+                                              _p(delta), k, part_stride, delta_scale, _p(mix), _p(write), _p(out), rows,
+                                              _stream()), "stream_sum")
+
+
+def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, tau: float, q_scale: float,
+             state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor, o: torch.Tensor, requests: int,
+             heads: int, dim: int, vdim: int) -> None:
+    """Gated linear attention over the rows of a step, request by request from and into its state row: per head
+    S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q * q_scale). proj holds q, k (heads * dim each) and v (heads *
+    vdim) from the given columns; z: float32 [rows, heads * dim]; state: float32 [slots, >= heads * vdim * dim], S kept
+    transposed; o: float32 contiguous [rows, heads * vdim]. See csrc/gla.cu."""
+    from .device import sm_count
+    _cuda(proj, z, state, q_start, state_slots, o)
+    _rows_contiguous(proj, "proj")
+    _rows_contiguous(z, "z")
+    rows = proj.shape[0]
+    if z.dtype != torch.float32 or z.shape[0] < rows or z.shape[1] < heads * dim or o.dtype != torch.float32 \
+            or not o.is_contiguous() or o.shape != (rows, heads * vdim):
+        raise InvalidArgument("gla_scan: z float32 [rows, heads * dim], o float32 contiguous [rows, heads * vdim]")
+    if max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
+        raise InvalidArgument("gla_scan: q, k or v lie outside the projection")
+    if dim > 512:
+        raise Unsupported(f"gla_scan: a state of {dim} rows has no kernel (512 at most)")
+    _state_rows(state, heads * dim * vdim, "gla_scan")
+    _check(_fn("gla", "dl_gla_scan")(dtype_code(proj.dtype), _p(proj), proj.stride(0), q_col, k_col, v_col, _p(z), z.stride(0),
+                                     tau, q_scale, _p(state), state.stride(0), _p(q_start), _p(state_slots), _p(o), requests,
+                                     heads, dim, vdim, sm_count(), _stream()), "gla_scan")
+
+
+MOE_MAX_EXPERTS = 256
+MOE_TILE_ROWS = 32
+MOE_TENSOR_CORES = os.environ.get("DYNALM_MOE_TC", "1") != "0"
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """The most row tiles the experts' products of a step can have (csrc/moe.cu)."""
+    return pairs // MOE_TILE_ROWS + min(experts, pairs)
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Per row of float32 router logits [tokens, experts]: softmax over all experts, the `keep` best of `groups` equal
+    groups of neighbouring experts (a group's score: its largest), the `top` best experts of those groups (ids int32
+    [tokens, top]) and their scores over their sum, times `scale` (weights float32 [tokens, top])."""
+    _cuda(logits, ids, weights)
+    _rows_contiguous(logits, "logits")
+    tokens, experts = logits.shape
+    if logits.dtype != torch.float32 or ids.dtype != torch.int32 or weights.dtype != torch.float32 \
+            or not ids.is_contiguous() or not weights.is_contiguous() or ids.numel() < tokens * top or weights.numel() < tokens * top:
+        raise InvalidArgument("moe_route: logits float32, ids int32 [tokens, top], weights float32 [tokens, top]")
+    if experts > MOE_MAX_EXPERTS or top > experts or groups <= 0 or experts % groups or not 0 < keep <= groups \
+            or top > keep * (experts // groups):
+        raise Unsupported(f"moe_route: {experts} experts in {groups} groups, {keep} kept, {top} a token")
+    _check(_fn("moe", "dl_moe_route")(_p(logits), logits.stride(0), tokens, experts, top, groups, keep, scale, _p(ids),
+                                      _p(weights), _stream()), "moe_route")
+
+
+def moe_group(ids: torch.Tensor, pairs: int, experts: int, place_of: torch.Tensor, pair_at: torch.Tensor,
+              tiles: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """The (token, expert) pairs of a step in the order of their experts: place_of[pair], pair_at[place] (int32, one per
+    pair), and the row tiles of the experts' products, tiles[i] = (expert, first place, places), n_tiles[0] of them."""
+    _cuda(ids, place_of, pair_at, tiles, n_tiles)
+    if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (ids, place_of, pair_at, tiles, n_tiles)) \
+            or min(ids.numel(), place_of.numel(), pair_at.numel()) < pairs or tiles.numel() < 3 * moe_max_tiles(pairs, experts):
+        raise InvalidArgument("moe_group: int32 arrays of one entry per pair, tiles of three per possible tile")
+    if experts > MOE_MAX_EXPERTS:
+        raise Unsupported(f"moe_group: {experts} experts ({MOE_MAX_EXPERTS} at most)")
+    _check(_fn("moe", "dl_moe_group")(_p(ids), pairs, experts, _p(place_of), _p(pair_at), _p(tiles), _p(n_tiles), _stream()),
+           "moe_group")
+
+
+def moe_linear(a: torch.Tensor, pair_at: Optional[torch.Tensor], top_div: int, w: torch.Tensor, c: torch.Tensor,
+               tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, act: str = "none") -> None:
+    """c[place] = act(a[row of place] w[expert of place]^T) for every place of every tile: w [experts, N, K], a rows of K
+    numbers (the row of a place is pair_at[place] // top_div, or the place itself when pair_at is None), c [places, N]
+    of a's dtype or float32. act: "none" or "relu2"."""
+    _cuda(a, pair_at, w, c, tiles, n_tiles)
+    _rows_contiguous(a, "a")
+    _rows_contiguous(c, "c")
+    if w.dim() != 3 or not w.is_contiguous() or w.dtype != a.dtype or a.shape[1] != w.shape[2] or c.shape[1] != w.shape[1] \
+            or c.dtype not in (a.dtype, torch.float32) or act not in ("none", "relu2"):
+        raise InvalidArgument("moe_linear: w [experts, N, K] of a's dtype, a [rows, K], c [places, N] of a's dtype or float32")
+    _check(_fn("moe", "dl_moe_linear")(dtype_code(a.dtype), dtype_code(c.dtype), _p(a), a.stride(0), _p(pair_at), top_div,
+                                       _p(w), w.shape[1], w.shape[2], _p(c), c.stride(0), _p(tiles), _p(n_tiles), max_tiles,
+                                       1 if act == "relu2" else 0, 1 if MOE_TENSOR_CORES else 0, _stream()), "moe_linear")
+
+
+def moe_combine(c: torch.Tensor, place_of: torch.Tensor, weights: torch.Tensor, top: int, y: torch.Tensor) -> None:
+    """y[t] = sum_k weights[t, k] * c[place_of[t * top + k]] in float32, in the order of k. c: float32 [places, width]."""
+    _cuda(c, place_of, weights, y)
+    tokens, width = y.shape
+    if c.dtype != torch.float32 or not c.is_contiguous() or c.shape[1] != width or not y.is_contiguous() \
+            or place_of.dtype != torch.int32 or weights.dtype != torch.float32:
+        raise InvalidArgument("moe_combine: c float32 [places, width], y contiguous [tokens, width]")
+    _check(_fn("moe", "dl_moe_combine")(dtype_code(y.dtype), _p(c), width, _p(place_of), _p(weights), top, _p(y), tokens,
+                                        _stream()), "moe_combine")

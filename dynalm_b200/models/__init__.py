@@ -1,2 +1,2 @@
 """Architectures; importing this package registers them."""
-from . import llama, rematar, rodelorn, todupel  # noqa: F401
+from . import bugapel, llama, rematar, rodelorn, todupel  # noqa: F401

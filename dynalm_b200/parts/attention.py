@@ -156,16 +156,28 @@ class PagedAttention:
 
 @register_mixer("gated_attention")
 class GatedNormedAttention(PagedAttention):
-    """Grouped-query attention with keys of head_dim and values of value_dim numbers, queries and keys normed over
-    their WHOLE projection before the heads are cut (one statistic for all H * d numbers of q, one for the G * d of k;
-    plain weights), a rotation of the first `rotary_dim` numbers of every head, a window, and an output gate: the
-    concatenated heads times sigmoid(W_g h) before the output projection. One product gives [q | k | v | gate].
+    """Grouped-query attention with keys of head_dim and values of value_dim numbers, a rotation of the first
+    `rotary_dim` numbers of every head, a window, and what its parameters switch on:
 
-    Parameters: num_heads, num_kv_heads, head_dim, value_dim, scale, window, eps, qk_norm ("projection" or "none"),
-    gated (bool), position. Tensors: q, k, v, o, and by the parameters q_norm, k_norm, gate.
+    qk_norm     "projection": queries and keys normed over their WHOLE projection before the heads are cut and before
+                the rotation (one statistic for all H * d numbers of q, one for the G * d of k; weights q_norm, k_norm);
+                "head": after the rotation every head of q and k is divided by its own root mean square (no weight);
+                "none".
+    gated       the concatenated heads times sigmoid(W_g h) before the output projection (one product gives
+                [q | k | v | gate]).
+    sink        "zero": the softmax's denominator holds one more term of score 0, which carries no value; "none".
+    keep_first  with a window: keys at positions below it stay visible behind the window, at their true positions.
+    position    "rotary" (pairs i, i + rotary_dim / 2) or, with qk_norm "head" or "none", "rotary_interleaved" (pairs 2i,
+                2i + 1).
+    Biases of the four projections are taken when the model has them (q_bias, k_bias, v_bias, o_bias).
+
+    Parameters: num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, eps, qk_norm, gated, sink,
+    position. Tensors: q, k, v, o, and by the parameters q_norm, k_norm, gate.
 
     Where keys and values have one size the cache is the plain attention's (two arrays) and so are the kernels that
-    read it; otherwise a token's keys and values form one record [k | v] in one array, read by the plain kernel."""
+    read it, as far as they know the mask and the softmax asked for; otherwise a token's keys and values form one record
+    [k | v] in one array, read by the plain kernel. With `keep_first` the pages behind the window are kept (the first
+    of them are still read)."""
 
     out_name = "mixer_out"     # the workspace buffer of the result; a mixer that holds this one may name another
 
@@ -180,6 +192,10 @@ class GatedNormedAttention(PagedAttention):
             "q_norm": TensorDecl((qw,), role="vector", required=normed, init="around_one"),
             "k_norm": TensorDecl((kw,), role="vector", required=normed, init="around_one"),
             "gate": TensorDecl((ow, spec.width), required=gated),
+            "q_bias": TensorDecl((qw,), role="vector", required=False, init="bias"),
+            "k_bias": TensorDecl((kw,), role="vector", required=False, init="bias"),
+            "v_bias": TensorDecl((vw,), role="vector", required=False, init="bias"),
+            "o_bias": TensorDecl((spec.width,), role="vector", required=False, init="bias"),
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
@@ -187,8 +203,10 @@ class GatedNormedAttention(PagedAttention):
             raise Unsupported(f"gated_attention: head_dim {spec.head_dim} and value_dim {spec.value_dim} must be at most 256")
         if spec.num_heads % spec.num_kv_heads:
             raise Unsupported(f"gated_attention: {spec.num_heads} heads do not divide into {spec.num_kv_heads} KV heads")
-        if spec.get("qk_norm", "none") not in ("projection", "none"):
-            raise Unsupported(f"gated_attention: no query/key norm '{spec.qk_norm}' (projection, none)")
+        if spec.get("qk_norm", "none") not in ("projection", "head", "none"):
+            raise Unsupported(f"gated_attention: no query/key norm '{spec.qk_norm}' (projection, head, none)")
+        if spec.get("sink", "none") not in ("zero", "none"):
+            raise Unsupported(f"gated_attention: no sink '{spec.sink}' (zero, none)")
         self.spec = spec
         self.rt = runtime
         self.q_width = spec.num_heads * spec.head_dim
@@ -196,31 +214,46 @@ class GatedNormedAttention(PagedAttention):
         self.v_width = spec.num_kv_heads * spec.value_dim
         self.o_width = spec.num_heads * spec.value_dim
         self.normed = spec.get("qk_norm", "none") == "projection"
+        self.head_normed = spec.get("qk_norm", "none") == "head"
+        self.sink = spec.get("sink", "none") == "zero"
+        self.window = int(spec.get("window", 0))
+        self.keep_first = int(spec.get("keep_first", 0)) if self.window > 0 else 0
         self.gated = bool(spec.get("gated", False))
         self.same = spec.head_dim == spec.value_dim          # keys and values of one size: the plain attention's cache
         mats = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["gate"]] if self.gated else [])
         self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        biases = [tensors.get("q_bias"), tensors.get("k_bias"), tensors.get("v_bias")]
         self.b_qkv = None
+        if any(b is not None for b in biases):
+            widths = [self.q_width, self.kv_width, self.v_width] + ([self.o_width] if self.gated else [])
+            self.b_qkv = torch.cat([b if b is not None else torch.zeros(w, dtype=torch.float32, device=runtime.device)
+                                    for b, w in zip(biases + [None], widths)]).contiguous()
         self.q_norm, self.k_norm = (tensors["q_norm"], tensors["k_norm"]) if self.normed else (None, None)
         self.w_o = tensors["o"]
-        self.b_o = None
+        self.b_o = tensors.get("o_bias")
         self.eps = float(spec.get("eps", 1e-6))
         pos = spec.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if pos is not None else None
-        if self.position is not None and self.position.table() is None:
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
+        if self.position is not None and self.position.table() is None and not self.interleaved:
             raise Unsupported("gated_attention: the rotation runs inside its kernel and takes a position encoding with a table")
+        if self.interleaved and self.normed:
+            raise Unsupported("gated_attention: the interleaved rotation goes with the norm per head or with none")
+        # the kernels of the plain attention's cache know a window and an ordinary softmax
+        self.plain_mask = not self.sink and self.keep_first == 0
 
     def step_plans(self) -> list:
-        return super().step_plans() if self.same else []
+        return super().step_plans() if self.same and self.plain_mask else []
 
     def graph_key(self, ctx) -> tuple:
-        return super().graph_key(ctx) if self.same and self.rt.dtype == torch.bfloat16 else ()
+        return super().graph_key(ctx) if self.same and self.plain_mask and self.rt.dtype == torch.bfloat16 else ()
 
     def cache_spec(self) -> Optional[CacheSpec]:
         s = self.spec
+        window = self.window if self.keep_first == 0 else 0      # kept first tokens: no page is given back
         if self.same:
-            return CacheSpec(kind="pages", entry_shape=(s.num_kv_heads, s.head_dim), tensors=2, window=s.get("window", 0))
-        return CacheSpec(kind="pages", entry_shape=(self.kv_width + self.v_width,), tensors=1, window=s.get("window", 0))
+            return CacheSpec(kind="pages", entry_shape=(s.num_kv_heads, s.head_dim), tensors=2, window=window)
+        return CacheSpec(kind="pages", entry_shape=(self.kv_width + self.v_width,), tensors=1, window=window)
 
     def _kv(self, cache):
         """(keys of the first token, elements between tokens, values of the first token, elements between tokens)."""
@@ -237,25 +270,43 @@ class GatedNormedAttention(PagedAttention):
             raise Unsupported("gated_attention: every run of the layer keeps a cache of its own")
         rows = x.shape[0]
         proj = rt.buffer("gattn_proj", (rows, self.w_qkv.shape[0]))
-        linear(x, self.w_qkv, proj)
-        inv_freq, rot, pos_scale = self.position.table() if self.position is not None else (None, 0, 1.0)
+        linear(x, self.w_qkv, proj, self.b_qkv)
         k_cache, k_row, v_cache, v_row = self._kv(cache)
-        ops.qk_proj_norm_cache(proj, self.q_norm, self.k_norm, self.eps, self.normed, inv_freq, rot, pos_scale,
-                               ctx.positions, ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row,
-                               s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size)
+        if self.normed or (not self.head_normed and not self.interleaved):
+            inv_freq, rot, pos_scale = self.position.table() if self.position is not None else (None, 0, 1.0)
+            ops.qk_proj_norm_cache(proj, self.q_norm, self.k_norm, self.eps, self.normed, inv_freq, rot, pos_scale,
+                                   ctx.positions, ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row,
+                                   s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size)
+        else:
+            # the rotation first (either layout), then every head by itself
+            if self.position is None:
+                inv_freq, rot = None, 0
+            elif self.interleaved:
+                inv_freq, rot = self.position.inv_freq, self.position.rotary_dim
+            else:
+                inv_freq, rot, pos_scale = self.position.table()
+                if pos_scale != 1.0:
+                    raise Unsupported("gated_attention: stretched positions go with the norm over the projection")
+            ops.qk_rot_head_norm_cache(proj, inv_freq, rot, self.interleaved, self.head_normed, self.eps, ctx.positions,
+                                       ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row, s.num_heads,
+                                       s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size)
         attn = rt.buffer("gattn_out", (rows, self.o_width))
         self.attend(proj, cache, ctx, attn)
         if self.gated:
             ops.sigmoid_gate(attn, proj[:, self.q_width + self.kv_width + self.v_width:])
-        return linear_partial(attn, self.w_o, rt, self.out_name)
+        if self.b_o is None:
+            return linear_partial(attn, self.w_o, rt, self.out_name)
+        out = rt.buffer(self.out_name, (rows, s.width))
+        linear(attn, self.w_o, out, self.b_o)
+        return out
 
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
         s = self.spec
-        if self.same:
+        if self.same and self.plain_mask:
             from ..kernels import attention as fast
             if fast.paged_attention(qkv, cache, ctx, out, s, self.rt):
                 return
         k_cache, k_row, v_cache, v_row = self._kv(cache)
         ops.paged_attention_generic_kv(qkv, k_cache, k_row, v_cache, v_row, cache.block_table, ctx.positions, ctx.row_slot,
                                        out, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
-                                       float(s.scale), s.get("window", 0))
+                                       float(s.scale), self.window, self.keep_first, self.sink)

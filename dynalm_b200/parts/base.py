@@ -9,6 +9,7 @@ registering it under its `kind` string; the model builder finds it through the r
     FeedForward    declare(spec), forward(x, ctx) -> y
     Norm           declare(spec), forward(residual, out, delta=..., rows=...)
     Position       (built by the mixer that uses it) table() / apply(q, k, positions)
+    Connection     declare(spec); the weights with which a sublayer reads and writes a stream of several parts
     Block          arrangement of the four above around the residual stream
 
 The reference has one fixed arrangement inside `Transformer::forward_batch`
@@ -94,14 +95,17 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITIONS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
+CONNECTIONS = _Registry("stream connection")
 
-REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITIONS}
+REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITIONS,
+              "connection": CONNECTIONS}
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position = POSITIONS.register
 register_block = BLOCKS.register
+register_connection = CONNECTIONS.register
 
 
 def registry_of(spec) -> _Registry:

@@ -6,6 +6,8 @@ parts fed from the same x. The residual stream is float32; the sum of a part's o
 fused into the norm that follows, so a block leaves its last output (the parallel one: both) pending.
 "post_norm": x <- norm1(a x + mixer(x)); x <- norm2(a x + ffn(x)): the sublayers read the stream itself and each
 norm closes its own sum, so nothing is left pending and the stream is always a normed row.
+"hyper_connections": the stream has several parts; a sublayer reads a weighted sum of them and every part becomes a
+mix of all parts plus its own share of the sublayer's result.
 """
 
 from __future__ import annotations
@@ -16,7 +18,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import build_part, register_block
+from .base import TensorDecl, build_part, register_block, register_connection
 
 
 @dataclass
@@ -29,8 +31,20 @@ class ResidualStream:
     pending_scale: float = 1.0
     pending2: Optional[torch.Tensor] = None
     as_input: Optional[torch.Tensor] = None      # x in the compute dtype, when the part that wrote x last also left that
+    # A stream of several parts: float32 [rows, parts * width], a row's parts one after the other; x is then stale until
+    # `flush` has summed them. `link` is the stream connection of the sublayer whose result is `pending`.
+    streams: Optional[torch.Tensor] = None
+    parts: int = 1
+    link: Optional[object] = None
 
     def flush(self) -> torch.Tensor:
+        if self.streams is not None:
+            link = self.link if self.pending is not None else None
+            ops.stream_sum(self.streams, self.parts, self.x, delta=self.pending, delta_scale=self.pending_scale,
+                           mix=link.mix if link is not None else None, write=link.write if link is not None else None)
+            self.streams, self.parts, self.link, self.pending = None, 1, None, None
+            self.flush_second()
+            return self.x
         if self.pending is not None:
             ops.residual_add(self.x, self.pending, self.pending_scale)
             self.pending = None
@@ -200,5 +214,79 @@ class SandwichNormBlock(Block):
         else:
             ops.norm_add_norm(stream.x, a, post.weight, post.eps)
         stream.pending_scale = 1.0
+        stream.as_input = None
+        return stream
+
+
+@register_connection("hyper")
+class HyperConnection:
+    """The weights with which one sublayer sits on a stream of n parts: it reads sum_s read[s] x_s, and its result y
+    changes every part at once, x_t <- sum_s mix[s, t] x_s + write[t] * y (mix is indexed [from, to]). Tensors: in [n],
+    out [n], mix [n, n]; float32."""
+
+    replay_safe = True     # it launches nothing itself
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec):
+        n = spec.streams
+        return {"in": TensorDecl((n,), role="vector", init="around_one"),
+                "out": TensorDecl((n,), role="vector", init="around_one"),
+                "mix": TensorDecl((n, n), role="vector", init="bias")}
+
+    def __init__(self, spec, tensors, runtime):
+        self.spec = spec
+        self.read = tensors["in"].contiguous()
+        self.write = tensors["out"].contiguous()
+        self.mix = tensors["mix"].contiguous()
+
+
+@register_block("hyper_connections")
+class HyperConnectionBlock(Block):
+    """parts: mixer_norm, mixer, mixer_link, and optionally ffn_norm, ffn, ffn_link; parameter: streams (n). The stream
+    is n parts, all equal to the embedding at the start; for each sublayer u = sum_s read[s] x_s, y = sublayer(norm(u)),
+    x_t <- sum_s mix[s, t] x_s + write[t] y. The update a sublayer leaves is applied by the norm kernel of the sublayer
+    that follows (in this layer or the next), which reads a row's parts once, writes them back and norms their weighted
+    sum; the model's final norm reads the plain sum of the parts the same way. The norms are of a kind that reads such a
+    stream (`forward_stream`; "layer")."""
+
+    def __init__(self, spec, store, runtime):
+        super().__init__(spec, store, runtime)
+        self.has_ffn = "ffn" in spec.parts
+        self.n = int(spec.streams)
+        if not 0 < self.n <= ops.STREAM_MAX_PARTS:
+            from ..errors import Unsupported
+            raise Unsupported(f"hyper_connections: {self.n} streams ({ops.STREAM_MAX_PARTS} at most)")
+
+    def last_link(self):
+        """The stream connection of the sublayer whose result this layer leaves pending."""
+        return self.ffn_link if self.has_ffn else self.mixer_link
+
+    def entry_tensors(self, stream: ResidualStream) -> list:
+        """The tensors of the layer in front that this layer's first norm reads (engine/launch_memo.py)."""
+        link = stream.link if stream.streams is not None and stream.pending is not None else None
+        return [link.mix, link.write] if link is not None else []
+
+    def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
+        rows, width = stream.x.shape
+        rt, n = self.rt, self.n
+        init = None
+        if stream.streams is None:                 # the first layer of its kind: every part starts as the stream so far
+            init = stream.flush()
+            stream.streams = rt.buffer("residual_parts", (rows, n * width), torch.float32)
+            stream.parts = n
+        elif stream.parts != n:
+            from ..errors import Unsupported
+            raise Unsupported("hyper_connections: layers of one model share the number of streams")
+        h = rt.buffer("normed", (rows, width))
+        self.mixer_norm.forward_stream(stream.streams, n, h, init=init, delta=stream.pending, link=stream.link,
+                                       read=self.mixer_link.read)
+        a = self.mixer.forward(h, ctx, cache, owns_cache)
+        stream.pending, stream.pending_scale, stream.link = a, 1.0, self.mixer_link
+        if self.has_ffn:
+            h = rt.buffer("normed", (rows, width))
+            self.ffn_norm.forward_stream(stream.streams, n, h, delta=a, link=self.mixer_link, read=self.ffn_link.read)
+            f = self.ffn.forward(h, ctx)
+            stream.pending, stream.link = f, self.ffn_link
         stream.as_input = None
         return stream

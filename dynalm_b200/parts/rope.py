@@ -76,7 +76,14 @@ class InterleavedRotaryEncoding:
         i = np.arange(spec.rotary_dim // 2, dtype=np.float64)
         self.spec = spec
         self.rotary_dim = spec.rotary_dim
-        self.frequencies = torch.from_numpy(np.power(float(spec.theta), -2.0 * i / spec.rotary_dim)).to(runtime.device)
+        freq = np.power(float(spec.theta), -2.0 * i / spec.rotary_dim)
+        if spec.get("factors") is not None:
+            if len(spec.factors) != spec.rotary_dim // 2:
+                raise Unsupported(f"rotary encoding has {len(spec.factors)} factors for {spec.rotary_dim // 2} pairs")
+            freq = freq / np.asarray(spec.factors, dtype=np.float64)
+        self.frequencies = torch.from_numpy(freq).to(runtime.device)
+        # the same in float32, for a kernel that forms the angle in float32 (csrc/qk_proj_norm.cu)
+        self.inv_freq = torch.from_numpy(freq.astype(np.float32)).to(runtime.device)
 
     def table(self):
         return None

@@ -129,8 +129,8 @@ def open_model_folder(path: str) -> ModelFolder:
             if name in where:
                 raise Corrupt(f"{f.path}: tensor '{name}' is also in {where[name].path}")
             where[name] = f
-    plan = arch.plan(config, present=set(where))
-    found = {name: f.entries[name].shape for name, f in where.items()}
+    found = {name: tuple(f.entries[name].shape) for name, f in where.items()}
+    plan = arch.plan(config, present=found)         # names, and shapes for a plan that reads a size from one
     check_tensors(path, plan, found)
     return ModelFolder(path, config_obj, arch, config, plan, files, where)
 
