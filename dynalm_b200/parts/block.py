@@ -232,7 +232,7 @@ class HyperConnection:
         n = spec.streams
         return {"in": TensorDecl((n,), role="vector", init="around_one"),
                 "out": TensorDecl((n,), role="vector", init="around_one"),
-                "mix": TensorDecl((n, n), role="vector", init="bias")}
+                "mix": TensorDecl((n, n), role="vector", init="near_identity")}
 
     def __init__(self, spec, tensors, runtime):
         self.spec = spec

@@ -74,9 +74,9 @@ class RoutedMLP:
         n_tiles = rt.flat("moe_n_tiles", 1, torch.int32)
         ops.moe_group(ids, pairs, E, place_of, pair_at, tiles, n_tiles)
         max_tiles = ops.moe_max_tiles(pairs, E)
-        act = rt.flat(f"moe_act_{s.inner}", most * s.inner, x.dtype)[:pairs * s.inner].view(pairs, s.inner)
+        act = rt.flat(f"moe_act_{top}_{s.inner}", most * s.inner, x.dtype)[:pairs * s.inner].view(pairs, s.inner)
         ops.moe_linear(x, pair_at, top, self.w_up, act, tiles, n_tiles, max_tiles, "relu2")
-        per_pair = rt.flat(f"moe_out_{s.width}", most * s.width, torch.float32)[:pairs * s.width].view(pairs, s.width)
+        per_pair = rt.flat(f"moe_out_{top}_{s.width}", most * s.width, torch.float32)[:pairs * s.width].view(pairs, s.width)
         ops.moe_linear(act, None, 1, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none")
         y = rt.buffer("ffn_out", (rows, s.width))
         ops.moe_combine(per_pair, place_of, weights, top, y)

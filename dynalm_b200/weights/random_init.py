@@ -117,6 +117,8 @@ def random_tensors(plan: ModelPlan, seed: int, dtype: torch.dtype = torch.bfloat
             t = seeded_normal(seed, name, numel, 1.0, NORM_STD)
         elif decl.init == "bias":
             t = seeded_normal(seed, name, numel, 0.0, BIAS_STD)
+        elif decl.init == "near_identity":
+            t = seeded_normal(seed, name, numel, 0.0, BIAS_STD).view(decl.shape) + torch.eye(decl.shape[0], decl.shape[1])
         else:
             t = seeded_normal(seed, name, numel, 0.0, MATRIX_STD)
         out[name] = t.view(decl.shape).to(dtype)

@@ -115,7 +115,7 @@ def attend(q, k, v, q_pos, k_pos, scale, window=0, keep_first=0, sink=False):
         js = [b for b in range(len(k_pos)) if visible(q_pos[a], k_pos[b], window, keep_first)]
         for h in range(H):
             g = h // (H // G)
-            s = np.array([q[a, h] @ k[b, g] for b in js]) * scale
+            s = (k[js, g] @ q[a, h]) * scale
             m = max(s.max(), 0.0) if sink else s.max()
             w = np.exp(s - m)
             den = w.sum() + (math.exp(-m) if sink else 0.0)
