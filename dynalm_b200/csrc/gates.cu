@@ -120,3 +120,26 @@ DL_EXPORT int dl_softcap(float* x, long long n, float cap, cudaStream_t stream) 
   dl::softcap_kernel<<<dl::blocks_for(static_cast<size_t>(n)), 256, 0, stream>>>(x, static_cast<size_t>(n), cap, 1.0f / cap);
   return dl::launch_status();
 }
+
+// x[r, c] += bias[c] over rows of ld elements (the bias of a projection whose product ran without one).
+namespace dl {
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, long long ld, const float* __restrict__ bias, int n, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / n;
+  const int c = static_cast<int>(i % n);
+  T* p = x + r * ld + c;
+  *p = from_float<T>(to_float(*p) + bias[c]);
+}
+}  // namespace dl
+
+DL_EXPORT int dl_add_bias(int dtype, void* x, long long ld, const float* bias, int rows, int n, cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  const size_t total = static_cast<size_t>(rows) * n;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (dtype == 0) dl::add_bias_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(x), ld, bias, n, total);
+  else if (dtype == 1) dl::add_bias_kernel<dl::bf16><<<blocks, 256, 0, stream>>>(static_cast<dl::bf16*>(x), ld, bias, n, total);
+  else return DL_ERR_UNSUPPORTED;
+  return dl::launch_status();
+}

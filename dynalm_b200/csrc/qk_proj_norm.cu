@@ -79,10 +79,10 @@ qk_proj_norm_kernel(T* __restrict__ proj, int stride, const float* __restrict__ 
 // The other order: turn first, then make every head of q and k a unit-RMS vector by itself (no weight), or leave it
 // as it is. One warp per unit, a unit being a query head, a key head or the values of a KV head. The pairs of the
 // rotation are (i, i + rot / 2) or, interleaved, (2i, 2i + 1); a pair (u, v) turns to (u cos a - v sin a, v cos a + u
-// sin a), a = position * inv_freq[i], in float32.
+// sin a), a = position * inv_freq[i], in float32. A bias of the projection (q | k | v) may be added on the way in.
 template <typename T>
 __global__ void __launch_bounds__(256)
-qk_rot_head_norm_kernel(T* __restrict__ proj, int stride, const float* __restrict__ inv_freq, int rot, int interleaved,
+qk_rot_head_norm_kernel(T* __restrict__ proj, int stride, const float* __restrict__ bias, const float* __restrict__ inv_freq, int rot, int interleaved,
                         int unit_norm, float eps, const int* __restrict__ positions, const int* __restrict__ row_slot,
                         const int* __restrict__ block_table, int max_blocks, T* __restrict__ k_cache, size_t k_row,
                         T* __restrict__ v_cache, size_t v_row, int rows, int H, int G, int d, int e, int page_size) {
@@ -103,22 +103,29 @@ qk_rot_head_norm_kernel(T* __restrict__ proj, int stride, const float* __restric
   }
   if (u >= H + G) {                                         // values: a copy into the token's place
     if (page < 0) return;
-    const T* v = base + H * d + G * d + (u - H - G) * e;
+    const int off = H * d + G * d + (u - H - G) * e;
+    const T* v = base + off;
     T* dst = v_cache + slot * v_row + static_cast<size_t>(u - H - G) * e;
-    for (int i = lane; i < e; i += 32) dst[i] = v[i];
+    if (bias != nullptr) {
+      for (int i = lane; i < e; i += 32) dst[i] = from_float<T>(to_float(v[i]) + bias[off + i]);
+    } else {
+      for (int i = lane; i < e; i += 32) dst[i] = v[i];
+    }
     return;
   }
-  T* src = base + (u < H ? u * d : H * d + (u - H) * d);
+  const int src_off = u < H ? u * d : H * d + (u - H) * d;
+  T* src = base + src_off;
+  const float* bsrc = bias != nullptr ? bias + src_off : nullptr;
   const int half = rot / 2;
   float x[PER], xp[PER];
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int i = lane + 32 * j;
-    x[j] = i < d ? to_float(src[i]) : 0.0f;
+    x[j] = i < d ? to_float(src[i]) + (bsrc != nullptr ? bsrc[i] : 0.0f) : 0.0f;
     xp[j] = 0.0f;
     if (i < rot) {
       const int partner = interleaved ? (i ^ 1) : (i < half ? i + half : i - half);
-      xp[j] = to_float(src[partner]);
+      xp[j] = to_float(src[partner]) + (bsrc != nullptr ? bsrc[partner] : 0.0f);
     }
   }
   __syncwarp();                                             // every lane has read before any lane writes in place
@@ -175,8 +182,8 @@ DL_EXPORT int dl_qk_proj_norm_cache(int dtype, void* proj, int stride, const flo
 
 // Rows [q: H*d | k: G*d | v: G*e | ...]: rotation first (rot numbers of every head, pairs by halves or interleaved),
 // then every head of q and k divided by its own root mean square (unit_norm) or left; q in place, k and v into the
-// pages. d at most 256.
-DL_EXPORT int dl_qk_rot_head_norm_cache(int dtype, void* proj, int stride, const float* inv_freq, int rot, int interleaved,
+// pages. bias: float32 [H*d + G*d + G*e] added to q | k | v first, or null. d at most 256.
+DL_EXPORT int dl_qk_rot_head_norm_cache(int dtype, void* proj, int stride, const float* bias, const float* inv_freq, int rot, int interleaved,
                                         int unit_norm, float eps, const int* positions, const int* row_slot,
                                         const int* block_table, int max_blocks, void* k_cache, long long k_row,
                                         void* v_cache, long long v_row, int rows, int H, int G, int d, int e, int page_size,
@@ -188,7 +195,7 @@ DL_EXPORT int dl_qk_rot_head_norm_cache(int dtype, void* proj, int stride, const
   const long long units = static_cast<long long>(rows) * (H + 2 * G);
   const unsigned blocks = static_cast<unsigned>((units + 7) / 8);
 #define DL_QK(T)                                                                                                          \
-  dl::qk_rot_head_norm_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<T*>(proj), stride, inv_freq, rot, interleaved,   \
+  dl::qk_rot_head_norm_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<T*>(proj), stride, bias, inv_freq, rot, interleaved, \
                                                              unit_norm, eps, positions, row_slot, block_table, max_blocks, \
                                                              static_cast<T*>(k_cache), static_cast<size_t>(k_row),         \
                                                              static_cast<T*>(v_cache), static_cast<size_t>(v_row), rows, H, \

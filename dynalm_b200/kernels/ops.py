@@ -80,8 +80,10 @@ _SIGNATURES = {
     "qk_proj_norm": {
         "dl_qk_proj_norm_cache": [_I, _P, _I, _P, _P, _F, _I, _P, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I,
                                   _I, _I, _P],
-        "dl_qk_rot_head_norm_cache": [_I, _P, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I,
+        "dl_qk_rot_head_norm_cache": [_I, _P, _I, _P, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I,
                                       _P]},
+    "attention_masked_flash": {
+        "dl_masked_flash_attention": [_P, _I, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P]},
     "layer_norm": {
         "dl_stream_layer_norm": [_I, _I, _P, _I, _I, _P, _P, _I, _L, _F, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
         "dl_stream_sum": [_I, _P, _I, _I, _P, _I, _L, _F, _P, _P, _P, _I, _P]},
@@ -96,7 +98,8 @@ _SIGNATURES = {
         "dl_gelu_mul": [_I, _P, _P, _I, _I, _P],
         "dl_sigmoid_gate": [_I, _P, _I, _P, _I, _I, _I, _P],
         "dl_scaled_sum": [_I, _P, _I, _L, _F, _I, _P, _I, _L, _F, _P, _L, _P],
-        "dl_softcap": [_P, _L, _F, _P]},
+        "dl_softcap": [_P, _L, _F, _P],
+        "dl_add_bias": [_I, _P, _L, _P, _I, _I, _P]},
     "norm_sandwich": {
         "dl_norm_add_norm": [_I, _I, _P, _P, _I, _L, _P, _F, _P, _F, _P, _I, _I, _P]},
     "attention_decode": {
@@ -1860,8 +1863,8 @@ def norm_add_norm(x: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, ep
 def qk_rot_head_norm_cache(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, interleaved: bool, unit_norm: bool,
                            eps: float, positions: torch.Tensor, row_slot: torch.Tensor, block_table: torch.Tensor,
                            k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int, heads: int, kv_heads: int,
-                           dim: int, vdim: int, page_size: int) -> None:
-    """Rows [q: H*d | k: G*d | v: G*e | ...] of a projection: the first `rot` numbers of every head of q and k turned by
+                           dim: int, vdim: int, page_size: int, bias: Optional[torch.Tensor] = None) -> None:
+    """Rows [q: H*d | k: G*d | v: G*e | ...] of a projection (plus `bias`, float32 over q | k | v, when given): the first `rot` numbers of every head of q and k turned by
     position (pairs i, i + rot/2, or 2i, 2i + 1 when interleaved), then every head divided by its own root mean square
     (unit_norm) or left; q written back in place, k and v written to the token's place in the cache (k_cache / v_cache
     point at the first token's keys / values, k_row / v_row elements lie between two tokens). See csrc/qk_proj_norm.cu."""
@@ -1873,9 +1876,12 @@ def qk_rot_head_norm_cache(proj: torch.Tensor, inv_freq: Optional[torch.Tensor],
         raise Unsupported(f"qk_rot_head_norm_cache: heads of {dim} numbers (256 at most)")
     if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
         raise InvalidArgument("qk_rot_head_norm_cache: inv_freq float32 [rot / 2]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() < heads * dim + kv_heads * (dim + vdim)):
+        raise InvalidArgument("qk_rot_head_norm_cache: bias float32 over q | k | v")
+    _cuda(bias)
     check_limits("qk_proj_norm", pages=k_cache.shape[0], requests=block_table.shape[0], rows=proj.shape[0])
     _check(_fn("qk_proj_norm", "dl_qk_rot_head_norm_cache")(
-        dtype_code(proj.dtype), _p(proj), proj.stride(0), _p(inv_freq), rot, 1 if interleaved else 0, 1 if unit_norm else 0,
+        dtype_code(proj.dtype), _p(proj), proj.stride(0), _p(bias), _p(inv_freq), rot, 1 if interleaved else 0, 1 if unit_norm else 0,
         eps, _p(positions), _p(row_slot), _p(block_table), block_table.stride(0), _p(k_cache), k_row, _p(v_cache), v_row,
         proj.shape[0], heads, kv_heads, dim, vdim, page_size, _stream()), "qk_rot_head_norm_cache")
 
@@ -2034,3 +2040,45 @@ def moe_combine(c: torch.Tensor, place_of: torch.Tensor, weights: torch.Tensor, 
         raise InvalidArgument("moe_combine: c float32 [places, width], y contiguous [tokens, width]")
     _check(_fn("moe", "dl_moe_combine")(dtype_code(y.dtype), _p(c), width, _p(place_of), _p(weights), top, _p(y), tokens,
                                         _stream()), "moe_combine")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[r, :] += bias over the rows of x (float32 bias), in place."""
+    _cuda(x, bias)
+    _rows_contiguous(x, "x")
+    if bias.dtype != torch.float32 or bias.numel() != x.shape[1]:
+        raise InvalidArgument("add_bias: bias float32 [columns of x]")
+    _check(_fn("gates", "dl_add_bias")(dtype_code(x.dtype), _p(x), x.stride(0), _p(bias), x.shape[0], x.shape[1], _stream()),
+           "add_bias")
+
+
+MASKED_FLASH_SIZES = {(d, d) for d in range(16, 129, 16)} | {(32, 16), (48, 32), (64, 32), (96, 48), (96, 64), (128, 64),
+                                                             (64, 128), (32, 64), (48, 16), (16, 32)}
+
+
+def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int,
+                           block_table: torch.Tensor, q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int,
+                           n_kv_heads: int, key_dim: int, value_dim: int, page_size: int, scale: float, window: int = 0,
+                           keep_first: int = 0, sink: bool = False) -> None:
+    """Flash attention of query tiles over the paged cache, bfloat16, with keys of key_dim and values of value_dim
+    numbers (a pair of MASKED_FLASH_SIZES), kept first tokens behind the window and an optional extra term exp(0) in the
+    denominator; see csrc/attention_masked_flash.cu. q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128,
+    first position). k_cache / v_cache point at the first token's keys / values, k_row / v_row elements between tokens."""
+    _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise Unsupported("masked flash attention: bfloat16 only")
+    if (key_dim, value_dim) not in MASKED_FLASH_SIZES or page_size & (page_size - 1) or n_heads % n_kv_heads:
+        raise Unsupported(f"masked flash attention: keys of {key_dim} and values of {value_dim}, page size {page_size}, "
+                          f"heads {n_heads}:{n_kv_heads}")
+    if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or q_tiles.data_ptr() % 16 \
+            or k_row % 8 or v_row % 8 or k_cache.data_ptr() % 16 or v_cache.data_ptr() % 16:
+        raise Unsupported("masked flash attention: q and cache rows must be 16-byte aligned, out rows 4-byte aligned")
+    if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
+        raise InvalidArgument("masked flash attention: q_tiles must be int32 [n_tiles, 4]")
+    check_limits("attention_masked_flash", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
+    _check(_fn("attention_masked_flash", "dl_masked_flash_attention")(
+        _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table), block_table.stride(0), _p(q_tiles),
+        n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, key_dim, value_dim, page_size, scale, window, int(keep_first),
+        1 if sink else 0, _stream()), "masked_flash_attention")

@@ -243,7 +243,10 @@ class GatedNormedAttention(PagedAttention):
         self.plain_mask = not self.sink and self.keep_first == 0
 
     def step_plans(self) -> list:
-        return super().step_plans() if self.same and self.plain_mask else []
+        if self.same and self.plain_mask:
+            return super().step_plans()
+        from ..kernels import attention as fast
+        return [fast.QUERY_TILES]                  # the masked flash kernel walks the step's query tiles
 
     def graph_key(self, ctx) -> tuple:
         return super().graph_key(ctx) if self.same and self.plain_mask and self.rt.dtype == torch.bfloat16 else ()
@@ -270,9 +273,11 @@ class GatedNormedAttention(PagedAttention):
             raise Unsupported("gated_attention: every run of the layer keeps a cache of its own")
         rows = x.shape[0]
         proj = rt.buffer("gattn_proj", (rows, self.w_qkv.shape[0]))
-        linear(x, self.w_qkv, proj, self.b_qkv)
+        by_projection = self.normed or (not self.head_normed and not self.interleaved)
+        # a bias joins in the kernel that turns and norms, where that kernel takes one; else in the product (the plain one)
+        linear(x, self.w_qkv, proj, self.b_qkv if (by_projection or self.gated) else None)
         k_cache, k_row, v_cache, v_row = self._kv(cache)
-        if self.normed or (not self.head_normed and not self.interleaved):
+        if by_projection:
             inv_freq, rot, pos_scale = self.position.table() if self.position is not None else (None, 0, 1.0)
             ops.qk_proj_norm_cache(proj, self.q_norm, self.k_norm, self.eps, self.normed, inv_freq, rot, pos_scale,
                                    ctx.positions, ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row,
@@ -289,19 +294,47 @@ class GatedNormedAttention(PagedAttention):
                     raise Unsupported("gated_attention: stretched positions go with the norm over the projection")
             ops.qk_rot_head_norm_cache(proj, inv_freq, rot, self.interleaved, self.head_normed, self.eps, ctx.positions,
                                        ctx.row_slot, cache.block_table, k_cache, k_row, v_cache, v_row, s.num_heads,
-                                       s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size)
+                                       s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
+                                       bias=None if self.gated else self.b_qkv)
         attn = rt.buffer("gattn_out", (rows, self.o_width))
         self.attend(proj, cache, ctx, attn)
         if self.gated:
             ops.sigmoid_gate(attn, proj[:, self.q_width + self.kv_width + self.v_width:])
         if self.b_o is None:
             return linear_partial(attn, self.w_o, rt, self.out_name)
-        out = rt.buffer(self.out_name, (rows, s.width))
-        linear(attn, self.w_o, out, self.b_o)
+        if attn.dtype == torch.float32:
+            out = rt.buffer(self.out_name, (rows, s.width))
+            linear(attn, self.w_o, out, self.b_o)
+            return out
+        # 16-bit operands: the product leaves float32 sums (whole, or split-K partial sums) and the bias joins those
+        from ..kernels.gemm import skinny_ok, use_stream
+        if use_stream(attn, self.w_o) or skinny_ok(attn, self.w_o):
+            out = linear_partial(attn, self.w_o, rt, self.out_name)
+            ops.add_bias(out[0] if out.dim() == 3 else out, self.b_o)
+            return out
+        out = rt.buffer(self.out_name + "_wide", (rows, s.width), torch.float32)
+        linear(attn, self.w_o, out)
+        ops.add_bias(out, self.b_o)
         return out
+
+    def _flash_applies(self, qkv: torch.Tensor, cache, ctx) -> bool:
+        """bfloat16, sizes the masked flash kernel has, a step built with the query tiles, aligned rows."""
+        from ..kernels import attention as fast
+        s = self.spec
+        return (qkv.dtype == torch.bfloat16 and (s.head_dim, s.value_dim) in ops.MASKED_FLASH_SIZES
+                and fast.query_tiles(ctx) is not None and cache.page_size & (cache.page_size - 1) == 0
+                and qkv.stride(0) % 8 == 0 and self.kv_width % 8 == 0 and self.v_width % 8 == 0)
 
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
         s = self.spec
+        if not (self.same and self.plain_mask) and self._flash_applies(qkv, cache, ctx):
+            from ..kernels import attention as fast
+            q_tiles, n_tiles, _, _ = fast.query_tiles(ctx)
+            k_cache, k_row, v_cache, v_row = self._kv(cache)
+            ops.masked_flash_attention(qkv, k_cache, k_row, v_cache, v_row, cache.block_table, q_tiles, n_tiles, out,
+                                       s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
+                                       float(s.scale), self.window, self.keep_first, self.sink)
+            return
         if self.same and self.plain_mask:
             from ..kernels import attention as fast
             if fast.paged_attention(qkv, cache, ctx, out, s, self.rt):

@@ -221,9 +221,69 @@ def test_attention_with_kept_first_tokens_and_a_sink(dtype, H, G, d, e, window, 
     rec = G * (d + e)
     ops.paged_attention_generic_kv(_t(qs.reshape(len(rows), H * d), dtype), cache, rec, cache.view(-1)[G * d:], rec, table,
                                    _ints(rows), _ints([1] * len(rows)), out, H, G, d, e, page, 1.0, window, keep, sink)
+    flash = None
+    if dtype == torch.bfloat16 and (d, e) in ops.MASKED_FLASH_SIZES:          # the tensor-core kernel, a tile of one row each
+        flash = torch.zeros(len(rows), H * e, dtype=dtype, device=DEV)
+        tiles = _ints([x for r, i in enumerate(rows) for x in (1, r, 1, i)])
+        ops.masked_flash_attention(_t(qs.reshape(len(rows), H * d), dtype), cache, rec, cache.view(-1)[G * d:], rec, table,
+                                   tiles, len(rows), flash, H, G, d, e, page, 1.0, window, keep, sink)
     for r, (i, j) in enumerate(zip(rows, targets)):
         want = plain.attend(qs[r:r + 1], k[:i + 1], v[:i + 1], [i], list(range(i + 1)), 1.0, window, keep, sink)
         _close(_np(out[r]).reshape(1, H, e), want, 2e-5 if dtype == torch.float32 else 2e-2, f"query {i} pointed at key {j}")
+        if flash is not None:
+            _close(_np(flash[r]).reshape(1, H, e), want, 2e-2, f"flash kernel, query {i} pointed at key {j}")
+
+
+@pytest.mark.parametrize("H,G,d,e,window,keep,sink", [(4, 2, 32, 16, 20, 3, False), (6, 1, 48, 32, 0, 0, True),
+                                                      (2, 2, 128, 128, 160, 64, False), (3, 3, 64, 64, 70, 2, True),
+                                                      (2, 1, 96, 48, 64, 65, False), (4, 4, 16, 16, 129, 1, True)])
+def test_masked_flash_attention_on_portions(H, G, d, e, window, keep, sink):
+    """A prompt in query tiles of up to 128 rows beside a tile that continues another request in the middle of a key
+    tile; every query points at a key at one of its edges in turn (the window's first key, the one before it, the last
+    kept token, the first that is not kept, position 0, itself)."""
+    from dynalm_b200.kernels import ops
+    rng = np.random.RandomState(d + window + keep)
+    n, page = 333, 16
+    q, k, v, cache, table = _attention_case(rng, n, H, G, d, e, torch.bfloat16, page)
+    w = window if window > 0 else 10 ** 9
+    qs = q.reshape(n, H, d).copy()
+    for i in range(n):
+        j = [i - w + 1, i - w, keep - 1, keep, 0, i][i % 6]
+        if 0 <= j <= i:
+            for h in range(H):
+                kk = k[j, h // (H // G)]
+                qs[i, h] = kk * ((4.0 if sink else 25.0) / max(1e-6, (kk ** 2).sum()))
+    qs = _np(_t(qs, torch.bfloat16))
+    # the rows of the step: positions 200..332 of the request first (a portion that starts inside a key tile), then 0..199
+    order = list(range(200, n)) + list(range(200))
+    tiles = [(1, 0, 128, 200), (1, 128, 5, 328), (1, 133, 128, 0), (1, 261, 72, 128)]
+    out = torch.zeros(n, H * e, dtype=torch.bfloat16, device=DEV)
+    rec = G * (d + e)
+    ops.masked_flash_attention(_t(qs[order].reshape(n, H * d), torch.bfloat16), cache, rec, cache.view(-1)[G * d:], rec, table,
+                               _ints([x for t in tiles for x in t]), len(tiles), out, H, G, d, e, page, 0.5, window, keep, sink)
+    want = plain.attend(qs, k, v, list(range(n)), list(range(n)), 0.5, window, keep, sink)
+    _close(_np(out).reshape(n, H, e), want[order], 2e-2, "portions")
+
+
+def test_a_bias_joins_before_the_rotation():
+    """The bias of q | k | v added inside the kernel that turns and norms: equal to a projection that carried it."""
+    from dynalm_b200.kernels import ops
+    rng = np.random.RandomState(5)
+    H, G, d, e, rot, page = 3, 1, 24, 16, 12, 8
+    rows = 6
+    width = H * d + G * (d + e)
+    proj0, bias = rng.randn(rows, width), rng.randn(width)
+    freq = _t(plain.frequencies(100.0, rot).astype(np.float32))
+    table = _ints(range(4)).view(1, 4)
+    outs = []
+    for fused in (True, False):
+        proj = _t(proj0 if fused else proj0 + bias)
+        cache = torch.zeros(4, page, G * (d + e), device=DEV)
+        ops.qk_rot_head_norm_cache(proj, freq, rot, True, True, 1e-5, _ints(range(rows)), _ints([0] * rows), table, cache,
+                                   G * (d + e), cache.view(-1)[G * d:], G * (d + e), H, G, d, e, page, bias=_t(bias) if fused else None)
+        outs.append((_np(proj[:, :H * d]), _np(cache)))
+    _close(outs[0][0], outs[1][0], 1e-5, "queries")
+    _close(outs[0][1], outs[1][1], 1e-5, "keys and values")
 
 
 def _gla_inputs(rng, n, H, d, e, dtype):
