@@ -417,6 +417,39 @@ def rodelorn_pair(name):
     return rodelorn, rematar
 
 
+# --workload bugapel: the Bugapel design (attention of two makes and gated linear attention over four residual streams,
+# a mixture of experts as feed-forward) beside Rodelorn, the closest design here (windowed attention beside a gated linear
+# recurrence, and a gated delta rule with a matrix state per head), at equal width and depth: a linear-attention layer
+# stands where a delta layer stands, an attention layer where a pair stands. The experts are sized so that the weights a
+# token uses in a feed-forward (top x 2 matrices) equal those of Rodelorn's gated feed-forward (3 matrices).
+BUGAPEL_SIZES = {
+    # name: (width, layer kinds (g: linear attention, a: attention, w: windowed attention), attention (heads, kv_heads,
+    #        dim, vdim, window, kept first), linear attention (heads, dim, vdim, rank), experts (count, top, groups, kept,
+    #        ff), rodelorn size)
+    "w2048_d128": (2048, "gagw", (16, 4, 128, 128, 1024, 4), (16, 128, 128, 64), (8, 2, 4, 2, 6144), "w2048_d128"),
+    "w4096_d128": (4096, "gw", (32, 8, 128, 128, 2048, 4), (32, 128, 128, 64), (8, 2, 4, 2, 10752), "w4096_d128"),
+    "w2048_d64": (2048, "gagw", (32, 8, 64, 64, 512, 4), (32, 64, 64, 64), (8, 2, 4, 2, 6144), "w2048_d64"),
+}
+
+
+def bugapel_pair(name):
+    width, kinds, a, g, x, rod = BUGAPEL_SIZES[name]
+    stretch = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+    full = {"heads": a[0], "kv_heads": a[1], "dim": a[2], "vdim": a[3], "scale": a[2] ** -0.5 * 8.0,
+            "rot": {"base": 500000.0, "dims": a[2], "scaling": stretch}}
+    windowed = {"heads": a[0], "kv_heads": a[1], "dim": a[2], "vdim": a[3], "scale": a[2] ** -0.5,
+                "rot": {"base": 10000.0, "dims": a[2]}, "mask": {"size": a[4], "keep_first": a[5]}}
+    linear = {"heads": g[0], "dim": g[1], "vdim": g[2], "tau": 16.0, "rank": g[3]}
+    mlp = {"kind": "moe", "expert": {"ff": x[4]},
+           "router": {"experts": x[0], "top": x[1], "scale": 1.0, "groups": {"count": x[2], "keep": x[3]}}}
+    mixers = {"g": ("gla", linear), "a": ("attention", full), "w": ("attention_2", windowed)}
+    bugapel = {"architecture": "Bugapel", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5},
+               "embedding": {"scale": 8.0}, "streams": 4, "logit_softcap": 30.0,
+               "layers": [{"type": mixers[k][0], "mixer": dict(mixers[k][1]), "mlp": dict(mlp)} for k in kinds]}
+    rodelorn, _ = rodelorn_pair(rod)
+    return bugapel, rodelorn
+
+
 def arch_compare(args, kernels: bool, design: str = "todupel"):
     """Prefill (one prompt of 2,048 tokens) and decode (batches of 8 and 64 holding 2,048 tokens each) of a design
     and of the model it is set beside (the Llama shape, or Rematar for Rodelorn) at equal size, timed with CUDA events; with `kernels`, instead, the device time of every kernel
@@ -431,9 +464,10 @@ def arch_compare(args, kernels: bool, design: str = "todupel"):
 
     peaks = load_peaks()
     T, HELD_HERE, K = 2048, 2048, max(8, min(args.steps, 64))
-    sizes = {"todupel": ARCH_SIZES, "rematar": REMATAR_SIZES, "rodelorn": RODELORN_SIZES}[design]
-    other = "rematar" if design == "rodelorn" else "llama"
-    out = {"metric": f"{design.capitalize()} beside {'Rematar' if other == 'rematar' else 'the Llama shape'} of equal size: prefill and decode tokens/s", "unit": "tokens/s",
+    sizes = {"todupel": ARCH_SIZES, "rematar": REMATAR_SIZES, "rodelorn": RODELORN_SIZES, "bugapel": BUGAPEL_SIZES}[design]
+    other = {"rodelorn": "rematar", "bugapel": "rodelorn"}.get(design, "llama")
+    beside = {"rematar": "Rematar", "rodelorn": "Rodelorn", "llama": "the Llama shape"}[other]
+    out = {"metric": f"{design.capitalize()} beside {beside} of equal size: prefill and decode tokens/s", "unit": "tokens/s",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, random token ids", "peaks": peaks,
            "config": {"prefill_tokens": T, "decode_context": HELD_HERE, "decode_steps": K, "vocab": ARCH_VOCAB,
                       "l2": "inputs larger than L2: the weights of a model exceed 126 MB"}, "sizes": {}}
@@ -450,6 +484,11 @@ def arch_compare(args, kernels: bool, design: str = "todupel"):
             rec = {"shape": {"width": width, "layers": kinds, "ssd": list(s), "latent_attention": list(a), "llama": list(l),
                              "rematar_ff": l[3] * 3 // 2}}
             pair = rematar_pair(size)
+        elif design == "bugapel":
+            width, kinds, a, g, x, rod = BUGAPEL_SIZES[size]
+            rec = {"shape": {"width": width, "layers": kinds, "attention": list(a), "linear_attention": list(g),
+                             "experts": list(x), "streams": 4, "rodelorn": rod}}
+            pair = bugapel_pair(size)
         else:
             width, kinds, d, a, r, ff, rem = RODELORN_SIZES[size]
             rec = {"shape": {"width": width, "layers": kinds, "delta": list(d), "attention": list(a), "recurrence": list(r),
@@ -529,10 +568,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels", "rematar", "rematar-kernels", "rodelorn", "rodelorn-kernels"] + sorted(SERVING), default="decode",
+    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels", "rematar", "rematar-kernels", "rodelorn", "rodelorn-kernels", "bugapel", "bugapel-kernels"] + sorted(SERVING), default="decode",
                     help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads; "
                          "todupel / rematar: that design beside the Llama shape of equal size; rodelorn: that design beside Rematar of "
-                         "equal size (<design>-kernels: per kernel)")
+                         "equal size; bugapel: that design beside Rodelorn of equal size (<design>-kernels: per kernel)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
     ap.add_argument("--no-serve", action="store_true", help="skip the points of the 3B and 8B serving workloads")
@@ -547,7 +586,7 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.workload.split("-")[0] in ("todupel", "rematar", "rodelorn"):
+    if args.workload.split("-")[0] in ("todupel", "rematar", "rodelorn", "bugapel"):
         return arch_compare(args, kernels=args.workload.endswith("-kernels"), design=args.workload.split("-")[0])
     if args.workload != "decode":
         return serving(args.workload, args.layers if args.layers != FULL_LAYERS else None)

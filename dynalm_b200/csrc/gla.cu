@@ -2,7 +2,8 @@
 //
 // Per token and head (key size d, value size e), all float32:
 //
-//   alpha_i = sigmoid(z_i)^(1 / tau) = exp(-softplus(-z_i) / tau)          (z: the decay's projection, float32)
+//   alpha_i = sigmoid(z_i)^(1 / tau) = exp(-softplus(-z_i) / tau)          (z: the decay's projection, float32; dl_gla_decay,
+//                                                                            once per token, in place)
 //   S <- diag(alpha) S + k v^T                                              (S: d x e, row i belongs to key channel i)
 //   o = S^T (q * q_scale)                                                   (read after the write)
 //
@@ -22,8 +23,8 @@ constexpr int GLA_TILE = 16;
 
 template <typename T, int R>
 __global__ void __launch_bounds__(256)
-gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, const float* __restrict__ z,
-                int z_stride, float inv_tau, float q_scale, float* __restrict__ state, size_t state_stride,
+gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, const float* __restrict__ alpha,
+                int a_stride, float q_scale, float* __restrict__ state, size_t state_stride,
                 const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ o, int H, int d,
                 int e, int P, int cols) {
   extern __shared__ __align__(16) float sm[];
@@ -60,9 +61,7 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
         const T* prow = proj + static_cast<size_t>(t0 + t) * stride;
         qv = to_float(prow[q_col + head * d + i]) * q_scale;
         kv = to_float(prow[k_col + head * d + i]);
-        const float zz = -z[static_cast<size_t>(t0 + t) * z_stride + head * d + i];
-        const float sp = zz > 20.0f ? zz : log1pf(expf(zz));          // softplus(-z) = -log sigmoid(z)
-        av = expf(-sp * inv_tau);
+        av = alpha[static_cast<size_t>(t0 + t) * a_stride + head * d + i];
       }
       s_q[x] = qv;
       s_k[x] = kv;
@@ -73,8 +72,8 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
       s_v[x] = c0 + c < e ? to_float(proj[static_cast<size_t>(t0 + t) * stride + v_col + head * e + c0 + c]) : 0.0f;
     }
     __syncthreads();
-    {                                             // every lane walks the tile (the shuffles name the whole warp)
-      const int clr = cl < cols ? cl : cols - 1;
+    if ((tid & ~31) / P < cols) {                 // warps that hold columns; all their lanes walk the tile (the shuffles
+      const int clr = cl < cols ? cl : cols - 1;  // name the whole warp), the other warps of the block only fetch
       for (int t = 0; t < nt; ++t) {
         const float v = s_v[t * cols + clr];
         const float* qa = s_q + t * Dp;
@@ -116,17 +115,36 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
   }
 }
 
+// z (+ bias) -> sigmoid(.)^(1 / tau), in place: exp(-softplus(-z) / tau), with softplus(x) = x for large x.
+__global__ void gla_decay_kernel(float* __restrict__ z, int stride, int cols, const float* __restrict__ bias, float inv_tau,
+                                 size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float* p = z + (i / cols) * stride + i % cols;
+  const float x = -(*p + (bias != nullptr ? bias[i % cols] : 0.0f));
+  const float sp = x > 20.0f ? x : log1pf(expf(x));
+  *p = expf(-sp * inv_tau);
+}
+
 }  // namespace dl
 
+DL_EXPORT int dl_gla_decay(float* z, int stride, int rows, int cols, const float* bias, float tau, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (!(tau > 0.0f)) return DL_ERR_UNSUPPORTED;
+  const size_t total = static_cast<size_t>(rows) * cols;
+  dl::gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(z, stride, cols, bias, 1.0f / tau, total);
+  return dl::launch_status();
+}
+
 // proj: rows of `stride` elements holding q (H * d numbers from column q_col), k (from k_col) and v (H * e from v_col).
-// z: float32 rows of z_stride numbers, H * d of them used. state: float32, a request's row state_stride numbers from the
+// alpha: float32 rows of a_stride numbers, H * d of them used (the decays, from dl_gla_decay). state: float32, a request's row state_stride numbers from the
 // next, the first H * e * d of it S transposed. q_start: requests + 1 row numbers. o: float32 [rows, H * e].
-DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, int k_col, int v_col, const float* z,
-                          int z_stride, float tau, float q_scale, float* state, long long state_stride, const int* q_start,
+DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, int k_col, int v_col, const float* alpha,
+                          int a_stride, float q_scale, float* state, long long state_stride, const int* q_start,
                           const int* state_slots, float* o, int requests, int H, int d, int e, int sm_count,
                           cudaStream_t stream) {
   if (requests <= 0) return 0;
-  if (H <= 0 || d <= 0 || d > 512 || e <= 0 || !(tau > 0.0f) || H > 65535 || requests > 65535 || (dtype != 0 && dtype != 1))
+  if (H <= 0 || d <= 0 || d > 512 || e <= 0 || H > 65535 || requests > 65535 || (dtype != 0 && dtype != 1))
     return DL_ERR_UNSUPPORTED;
   int P = 1;
   while (P * 16 < d) P <<= 1;                      // lanes a column: the fewest that leave a lane at most 16 rows
@@ -135,15 +153,17 @@ DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, in
   if (cols > e) cols = e;
   // fewer columns a block while the grid leaves SMs idle (a block keeps at least a warp's worth of lanes busy)
   while (cols > 1 && cols * P > 32 && static_cast<long long>((e + cols - 1) / cols) * H * requests < sm_count) cols = (cols + 1) / 2;
-  const int threads = ((cols * P + 31) / 32) * 32;
+  // a block is 256 threads whatever its columns need: all of them fetch a tile's q, k, decays and values (the fetch of a
+  // tile is a chain of dependent trips to memory, shorter the more threads share it), the first cols * P compute
+  const int threads = 256;
   const int Dp = P * R;
   const size_t smem = static_cast<size_t>(dl::GLA_TILE) * (3 * Dp + 2 * cols) * sizeof(float);
   dim3 grid((e + cols - 1) / cols, H, requests);
 #define DL_GLA(T, RR)                                                                                                    \
   do {                                                                                                                   \
     cudaFuncSetAttribute(dl::gla_scan_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    dl::gla_scan_kernel<T, RR><<<grid, threads, smem, stream>>>(static_cast<const T*>(proj), stride, q_col, k_col, v_col, z, \
-                                                                z_stride, 1.0f / tau, q_scale, state,                    \
+    dl::gla_scan_kernel<T, RR><<<grid, threads, smem, stream>>>(static_cast<const T*>(proj), stride, q_col, k_col, v_col, alpha, \
+                                                                a_stride, q_scale, state,                                \
                                                                 static_cast<size_t>(state_stride), q_start, state_slots, o, \
                                                                 H, d, e, P, cols);                                       \
   } while (0)

@@ -18,15 +18,48 @@ namespace dl {
 constexpr int LN_THREADS = 256;
 constexpr int LN_MAX_PARTS = 8;
 
-template <typename TO, typename TD>
+// V numbers at a time: V = 4 when every row starts on a 16-byte boundary (W a multiple of 4), else 1.
+template <typename T, int V> struct LnVec {
+  static __device__ __forceinline__ void load(const T* p, float* out) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = to_float(p[i]);
+  }
+};
+template <> struct LnVec<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float* out) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  }
+};
+template <> struct LnVec<bf16, 4> {
+  static __device__ __forceinline__ void load(const bf16* p, float* out) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+    out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+};
+template <int V> __device__ __forceinline__ void ln_store(float* p, const float* v) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else p[0] = v[0];
+}
+template <int V> __device__ __forceinline__ void ln_store(bf16* p, const float* v) {
+  if (V == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  } else {
+    p[0] = __float2bfloat16_rn(v[0]);
+  }
+}
+
+template <typename TO, typename TD, int V>
 __global__ void __launch_bounds__(LN_THREADS)
 stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float* __restrict__ init,
                          const TD* __restrict__ delta, int parts, size_t part_stride, float delta_scale,
                          const float* __restrict__ mix, const float* __restrict__ outw, const float* __restrict__ inw,
                          const float* __restrict__ w, const float* __restrict__ b, float eps, TO* __restrict__ out,
                          const int* __restrict__ rows_idx, int total_rows) {
-  extern __shared__ float su[];                 // u of the row, then 33 floats for the block sums
-  float* red = su + W;
+  extern __shared__ __align__(16) float su[];   // u of the row, then 33 floats for the block sums
+  float* red = su + ((W + 3) & ~3);
   __shared__ float s_mix[LN_MAX_PARTS * LN_MAX_PARTS], s_out[LN_MAX_PARTS], s_in[LN_MAX_PARTS];
   const int tid = threadIdx.x;
   const int row = rows_idx != nullptr ? ck_row(rows_idx[blockIdx.x], total_rows) : static_cast<int>(blockIdx.x);
@@ -40,48 +73,76 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
   float* xrow = streams + static_cast<size_t>(row) * S * W;
   const bool update = delta != nullptr;
   float sum = 0.0f;
-  for (int c = tid; c < W; c += LN_THREADS) {
-    float x[LN_MAX_PARTS];
+  for (int c = tid * V; c < W; c += LN_THREADS * V) {
+    float x[LN_MAX_PARTS][V];
     if (init != nullptr) {
-      const float v = init[static_cast<size_t>(row) * W + c];
+      float v[V];
+      LnVec<float, V>::load(init + static_cast<size_t>(row) * W + c, v);
 #pragma unroll
-      for (int s = 0; s < LN_MAX_PARTS; ++s) x[s] = v;
+      for (int s = 0; s < LN_MAX_PARTS; ++s)
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[s][i] = v[i];
     } else {
 #pragma unroll
-      for (int s = 0; s < LN_MAX_PARTS; ++s) x[s] = s < S ? xrow[static_cast<size_t>(s) * W + c] : 0.0f;
+      for (int s = 0; s < LN_MAX_PARTS; ++s) {
+        if (s < S) {
+          LnVec<float, V>::load(xrow + static_cast<size_t>(s) * W + c, x[s]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) x[s][i] = 0.0f;
+        }
+      }
     }
-    float u = 0.0f;
+    float u[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) u[i] = 0.0f;
     if (update) {
-      float y = 0.0f;
-      for (int p = 0; p < parts; ++p) y += to_float(delta[p * part_stride + static_cast<size_t>(row) * W + c]);
-      y *= delta_scale;
+      float y[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) y[i] = 0.0f;
+      for (int p = 0; p < parts; ++p) {
+        float d[V];
+        LnVec<TD, V>::load(delta + p * part_stride + static_cast<size_t>(row) * W + c, d);
+#pragma unroll
+        for (int i = 0; i < V; ++i) y[i] += d[i];
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) y[i] *= delta_scale;
 #pragma unroll
       for (int t = 0; t < LN_MAX_PARTS; ++t) {
         if (t < S) {
-          float v = 0.0f;
-          if (mix != nullptr) {
+          float v[V];
 #pragma unroll
-            for (int s = 0; s < LN_MAX_PARTS; ++s)
-              if (s < S) v = fmaf(s_mix[s * S + t], x[s], v);
-          } else {
-            v = x[t];
+          for (int i = 0; i < V; ++i) {
+            float a = 0.0f;
+            if (mix != nullptr) {
+#pragma unroll
+              for (int s = 0; s < LN_MAX_PARTS; ++s)
+                if (s < S) a = fmaf(s_mix[s * S + t], x[s][i], a);
+            } else {
+              a = x[t][i];
+            }
+            v[i] = fmaf(s_out[t], y[i], a);
+            u[i] = fmaf(s_in[t], v[i], u[i]);
           }
-          v = fmaf(s_out[t], y, v);
-          if (write_back) xrow[static_cast<size_t>(t) * W + c] = v;
-          u = fmaf(s_in[t], v, u);
+          if (write_back) ln_store<V>(xrow + static_cast<size_t>(t) * W + c, v);
         }
       }
     } else {
 #pragma unroll
       for (int t = 0; t < LN_MAX_PARTS; ++t) {
         if (t < S) {
-          if (init != nullptr && write_back) xrow[static_cast<size_t>(t) * W + c] = x[t];
-          u = fmaf(s_in[t], x[t], u);
+          if (init != nullptr && write_back) ln_store<V>(xrow + static_cast<size_t>(t) * W + c, x[t]);
+#pragma unroll
+          for (int i = 0; i < V; ++i) u[i] = fmaf(s_in[t], x[t][i], u[i]);
         }
       }
     }
-    su[c] = u;
-    sum += u;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      su[c + i] = u[i];
+      sum += u[i];
+    }
   }
   const float mean = block_sum(sum, red) / static_cast<float>(W);
   float sq = 0.0f;
@@ -92,8 +153,14 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
   const float rstd = 1.0f / sqrtf(block_sum(sq, red) / static_cast<float>(W) + eps);
   if (out != nullptr) {
     TO* orow = out + static_cast<size_t>(blockIdx.x) * W;
-    for (int c = tid; c < W; c += LN_THREADS)
-      orow[c] = from_float<TO>((su[c] - mean) * rstd * w[c] + (b != nullptr ? b[c] : 0.0f));
+    for (int c = tid * V; c < W; c += LN_THREADS * V) {
+      float v[V], wv[V], bv[V];
+      LnVec<float, V>::load(w + c, wv);
+      if (b != nullptr) LnVec<float, V>::load(b + c, bv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] = (su[c + i] - mean) * rstd * wv[i] + (b != nullptr ? bv[i] : 0.0f);
+      ln_store<V>(orow + c, v);
+    }
   }
 }
 
@@ -138,11 +205,22 @@ DL_EXPORT int dl_stream_layer_norm(int out_dtype, int delta_dtype, float* stream
                                    cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (S <= 0 || S > dl::LN_MAX_PARTS || W <= 0 || W > 49152 / 4 - 64 || (delta != nullptr && parts <= 0)) return DL_ERR_UNSUPPORTED;
-  const size_t smem = (static_cast<size_t>(W) + 33) * sizeof(float);
+  const size_t smem = (static_cast<size_t>((W + 3) & ~3) + 33) * sizeof(float);
+  // four numbers at a time when every row and every partial sum starts on a 16-byte boundary
+  const bool wide = W % 4 == 0 && part_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(streams) | reinterpret_cast<uintptr_t>(init) |
+                    reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b) |
+                    reinterpret_cast<uintptr_t>(out)) & 15) == 0;
 #define DL_LN(TO, TD)                                                                                                   \
-  dl::stream_layer_norm_kernel<TO, TD><<<n_out, dl::LN_THREADS, smem, stream>>>(                                       \
-      streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix, outw, \
-      inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows)
+  do {                                                                                                                  \
+    if (wide)                                                                                                           \
+      dl::stream_layer_norm_kernel<TO, TD, 4><<<n_out, dl::LN_THREADS, smem, stream>>>(                                 \
+          streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix, \
+          outw, inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows);                                           \
+    else                                                                                                                \
+      dl::stream_layer_norm_kernel<TO, TD, 1><<<n_out, dl::LN_THREADS, smem, stream>>>(                                 \
+          streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix, \
+          outw, inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows);                                           \
+  } while (0)
   if (out_dtype == 0 && delta_dtype == 0) DL_LN(float, float);
   else if (out_dtype == 1 && delta_dtype == 1) DL_LN(dl::bf16, dl::bf16);
   else if (out_dtype == 1 && delta_dtype == 0) DL_LN(dl::bf16, float);

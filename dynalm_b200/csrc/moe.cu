@@ -9,14 +9,16 @@
 //                    stands at every place, and the list of row tiles (expert, first place, places) for the products.
 //   dl_moe_linear    C[place] = act(A[row of place] W_e^T) for every place of every tile, W_e the matrix of the tile's
 //                    expert: a plain tiled product with float32 accumulation in a fixed order of k (any dtype), and one on
-//                    the tensor cores for bfloat16 (mma.sync m16n8k16, float32 accumulation).
+//                    the tensor cores for bfloat16 (mma.sync m16n8k16, float32 accumulation), with tiles of 32 places for
+//                    steps that bring an expert few and of 128 for steps that bring it many.
 //   dl_moe_combine   y[t] = sum_k weight[t, k] * C[place of pair (t, k)], float32, in the order of k.
 #include "common.cuh"
 
 namespace dl {
 
 constexpr int MOE_MAX_EXPERTS = 256;
-constexpr int MOE_TM = 32;          // places a tile
+constexpr int MOE_TM = 32;          // places a tile of the kernels for few places an expert
+constexpr int MOE_TM_WIDE = 128;    // places a tile of the kernel for many
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int stride, int tokens, int E, int top, int groups,
                                  int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
@@ -77,7 +79,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int stride, i
 // places) for i < n_tiles[0].
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ place_of, int* __restrict__ pair_at,
-                 int* __restrict__ tiles, int* __restrict__ n_tiles) {
+                 int* __restrict__ tiles, int* __restrict__ n_tiles, int TM) {
   __shared__ int count[MOE_MAX_EXPERTS], first[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS], tile0[MOE_MAX_EXPERTS + 1];
   const int tid = threadIdx.x;
   for (int i = tid; i < E; i += blockDim.x) { count[i] = 0; cursor[i] = 0; }
@@ -90,7 +92,7 @@ moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict_
       first[i] = at;
       tile0[i] = tl;
       at += count[i];
-      tl += (count[i] + MOE_TM - 1) / MOE_TM;
+      tl += (count[i] + TM - 1) / TM;
     }
     first[E] = at;
     tile0[E] = tl;
@@ -106,12 +108,12 @@ moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict_
     pair_at[place] = p;
   }
   for (int i = tid; i < E; i += blockDim.x) {
-    const int nt = (count[i] + MOE_TM - 1) / MOE_TM;
+    const int nt = (count[i] + TM - 1) / TM;
     for (int j = 0; j < nt; ++j) {
       int* tl = tiles + 3 * (tile0[i] + j);
       tl[0] = i;
-      tl[1] = first[i] + j * MOE_TM;
-      tl[2] = min(MOE_TM, count[i] - j * MOE_TM);
+      tl[1] = first[i] + j * TM;
+      tl[2] = min(TM, count[i] - j * TM);
     }
   }
 }
@@ -264,6 +266,97 @@ moe_linear_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict
       }
 }
 
+// bfloat16 on the tensor cores for many places an expert: tile = 128 places x 128 features, 8 warps as 2 x 4 (a warp
+// takes 64 places x 32 features: four m16 by four n8 fragments), k in steps of 32 through a cp.async double buffer,
+// fragments by ldmatrix. The matrix of the tile's expert is read once per 128 places instead of once per 32.
+__device__ __forceinline__ void moe_cp16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+moe_linear_wide_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
+                       const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
+                       const int* __restrict__ n_tiles, int act) {
+  constexpr int TM = MOE_TM_WIDE, TN = 128, TK = 32, LD = TK + 8;
+  __shared__ __align__(16) bf16 As[2][TM][LD];
+  __shared__ __align__(16) bf16 Bs[2][TN][LD];
+  __shared__ int src[TM];
+  if (static_cast<int>(blockIdx.y) >= n_tiles[0]) return;
+  const int* tl = tiles + 3 * blockIdx.y;
+  const int ex = tl[0], p0 = tl[1], np = tl[2];
+  const int n0 = blockIdx.x * TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wn = warp & 3;               // the warp's 64 places and 32 features
+  if (tid < TM) src[tid] = tid < np ? (pair_at != nullptr ? pair_at[p0 + tid] / top_div : p0 + tid) : -1;
+  __syncthreads();
+  const bf16* wx = w + static_cast<size_t>(ex) * N * K;
+  // a stage: A and B 128 x 32 numbers = 512 pieces of 16 bytes each, two a thread
+  auto load = [&](int stage, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int x = tid + 256 * i, r = x >> 2, piece = x & 3;
+      const bool ok = src[r] >= 0;
+      moe_cp16(&As[stage][r][piece * 8], a + static_cast<size_t>(ok ? src[r] : 0) * lda + k0 + piece * 8, ok);
+      const bool okb = n0 + r < N;
+      moe_cp16(&Bs[stage][r][piece * 8], wx + static_cast<size_t>(okb ? n0 + r : 0) * K + k0 + piece * 8, okb);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  float acc[4][4][4] = {};
+  const int steps = K / TK;
+  load(0, 0);
+  for (int s = 0; s < steps; ++s) {
+    const int st = s & 1;
+    if (s + 1 < steps) {
+      load(st ^ 1, (s + 1) * TK);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t af[4][4], bfr[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 4; ++mi)
+        moe_ldmatrix_x4(af[mi], &As[st][wm * 64 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nj = 0; nj < 2; ++nj)       // two n8 fragments per ldmatrix.x4
+        moe_ldmatrix_x4(bfr[nj], &Bs[st][wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) {
+          const uint32_t b2[2] = {bfr[ni >> 1][(ni & 1) * 2], bfr[ni >> 1][(ni & 1) * 2 + 1]};
+          mma_bf16_16816(acc[mi][ni], af[mi], b2);
+        }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = wm * 64 + mi * 16 + g + 8 * h;
+        const int n = n0 + wn * 32 + ni * 8 + q * 2;
+        if (r >= np) continue;
+        TO* dst = c + static_cast<size_t>(p0 + r) * ldc + n;
+        if (n < N) dst[0] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h], act));
+        if (n + 1 < N) dst[1] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h + 1], act));
+      }
+}
+
 template <typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ c, int width, const int* __restrict__ place_of,
                                    const float* __restrict__ weights, int top, TO* __restrict__ y, size_t total) {
@@ -290,23 +383,40 @@ DL_EXPORT int dl_moe_route(const float* logits, int stride, int tokens, int E, i
 }
 
 DL_EXPORT int dl_moe_group(const int* ids, int pairs, int E, int* place_of, int* pair_at, int* tiles, int* n_tiles,
-                           cudaStream_t stream) {
+                           int tile_rows, cudaStream_t stream) {
   if (pairs <= 0) return 0;
-  if (E <= 0 || E > dl::MOE_MAX_EXPERTS) return DL_ERR_UNSUPPORTED;
-  dl::moe_group_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, place_of, pair_at, tiles, n_tiles);
+  if (E <= 0 || E > dl::MOE_MAX_EXPERTS || (tile_rows != dl::MOE_TM && tile_rows != dl::MOE_TM_WIDE)) return DL_ERR_UNSUPPORTED;
+  dl::moe_group_kernel<<<1, 1024, 0, stream>>>(ids, pairs, E, place_of, pair_at, tiles, n_tiles, tile_rows);
   return dl::launch_status();
 }
 
 // dtype of a and w: 0 float32, 1 bfloat16; out_dtype of c likewise. pair_at null: the rows of a are the places
 // themselves; else the row of a place is pair_at[place] / top_div. act: 0 none, 1 squared ReLU. tensor_cores: use the
 // mma.sync kernel where it applies (bfloat16, K a multiple of 32, rows of a and w on 16-byte boundaries).
+// tile_rows: the places a tile as dl_moe_group was told: 32, or 128 for the wide tensor-core kernel (bfloat16 only).
 DL_EXPORT int dl_moe_linear(int dtype, int out_dtype, const void* a, int lda, const int* pair_at, int top_div, const void* w,
                             int N, int K, void* c, int ldc, const int* tiles, const int* n_tiles, int max_tiles, int act,
-                            int tensor_cores, cudaStream_t stream) {
+                            int tensor_cores, int tile_rows, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N <= 0 || K <= 0 || top_div <= 0 || max_tiles > 65535) return DL_ERR_UNSUPPORTED;
-  if (dtype == 1 && tensor_cores && K % 32 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
-      (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+  const bool tc_ok = dtype == 1 && tensor_cores && K % 32 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  if (tile_rows == dl::MOE_TM_WIDE) {
+    if (!tc_ok) return DL_ERR_UNSUPPORTED;
+    dim3 grid((N + 127) / 128, max_tiles);
+    if (out_dtype == 1)
+      dl::moe_linear_wide_kernel<dl::bf16><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
+                                                                      static_cast<const dl::bf16*>(w), N, K,
+                                                                      static_cast<dl::bf16*>(c), ldc, tiles, n_tiles, act);
+    else if (out_dtype == 0)
+      dl::moe_linear_wide_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
+                                                                   static_cast<const dl::bf16*>(w), N, K, static_cast<float*>(c),
+                                                                   ldc, tiles, n_tiles, act);
+    else return DL_ERR_UNSUPPORTED;
+    return dl::launch_status();
+  }
+  if (tile_rows != dl::MOE_TM) return DL_ERR_UNSUPPORTED;
+  if (tc_ok) {
     dim3 grid((N + 127) / 128, max_tiles);
     if (out_dtype == 1)
       dl::moe_linear_mma_kernel<dl::bf16><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,

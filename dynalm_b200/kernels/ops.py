@@ -88,11 +88,12 @@ _SIGNATURES = {
         "dl_stream_layer_norm": [_I, _I, _P, _I, _I, _P, _P, _I, _L, _F, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
         "dl_stream_sum": [_I, _P, _I, _I, _P, _I, _L, _F, _P, _P, _P, _I, _P]},
     "gla": {
-        "dl_gla_scan": [_I, _P, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P]},
+        "dl_gla_decay": [_P, _I, _I, _I, _P, _F, _P],
+        "dl_gla_scan": [_I, _P, _I, _I, _I, _I, _P, _I, _F, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P]},
     "moe": {
         "dl_moe_route": [_P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
-        "dl_moe_group": [_P, _I, _I, _P, _P, _P, _P, _P],
-        "dl_moe_linear": [_I, _I, _P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P],
+        "dl_moe_group": [_P, _I, _I, _P, _P, _P, _P, _I, _P],
+        "dl_moe_linear": [_I, _I, _P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
         "dl_moe_combine": [_I, _P, _I, _P, _P, _I, _P, _I, _P]},
     "gates": {
         "dl_gelu_mul": [_I, _P, _P, _I, _I, _P],
@@ -1950,10 +1951,11 @@ def stream_sum(streams: torch.Tensor, parts: int, out: torch.Tensor, delta: Opti
 
 def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, tau: float, q_scale: float,
              state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor, o: torch.Tensor, requests: int,
-             heads: int, dim: int, vdim: int) -> None:
+             heads: int, dim: int, vdim: int, z_bias: Optional[torch.Tensor] = None) -> None:
     """Gated linear attention over the rows of a step, request by request from and into its state row: per head
     S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q * q_scale). proj holds q, k (heads * dim each) and v (heads *
-    vdim) from the given columns; z: float32 [rows, heads * dim]; state: float32 [slots, >= heads * vdim * dim], S kept
+    vdim) from the given columns; z: float32 [rows, heads * dim] (plus z_bias, float32 [heads * dim], when given), turned into the
+    decays in place; state: float32 [slots, >= heads * vdim * dim], S kept
     transposed; o: float32 contiguous [rows, heads * vdim]. See csrc/gla.cu."""
     from .device import sm_count
     _cuda(proj, z, state, q_start, state_slots, o)
@@ -1965,22 +1967,36 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Te
         raise InvalidArgument("gla_scan: z float32 [rows, heads * dim], o float32 contiguous [rows, heads * vdim]")
     if max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
         raise InvalidArgument("gla_scan: q, k or v lie outside the projection")
-    if dim > 512:
-        raise Unsupported(f"gla_scan: a state of {dim} rows has no kernel (512 at most)")
+    if dim > 512 or not tau > 0:
+        raise Unsupported(f"gla_scan: a state of {dim} rows (512 at most), tau {tau} (positive)")
     _state_rows(state, heads * dim * vdim, "gla_scan")
+    if z_bias is not None and (z_bias.dtype != torch.float32 or z_bias.numel() != heads * dim):
+        raise InvalidArgument("gla_scan: z_bias float32 [heads * dim]")
+    _cuda(z_bias)
+    _check(_fn("gla", "dl_gla_decay")(_p(z), z.stride(0), rows, heads * dim, _p(z_bias), tau, _stream()), "gla_decay")
     _check(_fn("gla", "dl_gla_scan")(dtype_code(proj.dtype), _p(proj), proj.stride(0), q_col, k_col, v_col, _p(z), z.stride(0),
-                                     tau, q_scale, _p(state), state.stride(0), _p(q_start), _p(state_slots), _p(o), requests,
+                                     q_scale, _p(state), state.stride(0), _p(q_start), _p(state_slots), _p(o), requests,
                                      heads, dim, vdim, sm_count(), _stream()), "gla_scan")
 
 
 MOE_MAX_EXPERTS = 256
-MOE_TILE_ROWS = 32
+MOE_TILE_ROWS = 32          # places a tile of the kernels for few places an expert
+MOE_WIDE_TILE_ROWS = 128    # of the wide tensor-core kernel
+MOE_WIDE_FROM = int(os.environ.get("DYNALM_MOE_WIDE_FROM", "48"))     # places an expert on average from which tiles are wide
 MOE_TENSOR_CORES = os.environ.get("DYNALM_MOE_TC", "1") != "0"
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
     """The most row tiles the experts' products of a step can have (csrc/moe.cu)."""
-    return pairs // MOE_TILE_ROWS + min(experts, pairs)
+    return pairs // tile_rows + min(experts, pairs)
+
+
+def moe_tile_rows(pairs: int, experts: int, a: torch.Tensor, widths) -> int:
+    """Places a tile for a step of `pairs` pairs: 128 where the wide tensor-core kernel applies (bfloat16, every inner
+    size in `widths` a multiple of 32) and an expert gets enough places on average, else 32."""
+    wide = (MOE_TENSOR_CORES and a.dtype == torch.bfloat16 and all(w % 32 == 0 for w in widths)
+            and pairs >= MOE_WIDE_FROM * experts)
+    return MOE_WIDE_TILE_ROWS if wide else MOE_TILE_ROWS
 
 
 def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float, ids: torch.Tensor,
@@ -2002,21 +2018,23 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: flo
 
 
 def moe_group(ids: torch.Tensor, pairs: int, experts: int, place_of: torch.Tensor, pair_at: torch.Tensor,
-              tiles: torch.Tensor, n_tiles: torch.Tensor) -> None:
+              tiles: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int = MOE_TILE_ROWS) -> None:
     """The (token, expert) pairs of a step in the order of their experts: place_of[pair], pair_at[place] (int32, one per
-    pair), and the row tiles of the experts' products, tiles[i] = (expert, first place, places), n_tiles[0] of them."""
+    pair), and the row tiles of the experts' products, tiles[i] = (expert, first place, places <= tile_rows), n_tiles[0]
+    of them."""
     _cuda(ids, place_of, pair_at, tiles, n_tiles)
     if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (ids, place_of, pair_at, tiles, n_tiles)) \
-            or min(ids.numel(), place_of.numel(), pair_at.numel()) < pairs or tiles.numel() < 3 * moe_max_tiles(pairs, experts):
+            or min(ids.numel(), place_of.numel(), pair_at.numel()) < pairs or tiles.numel() < 3 * moe_max_tiles(pairs, experts, tile_rows):
         raise InvalidArgument("moe_group: int32 arrays of one entry per pair, tiles of three per possible tile")
     if experts > MOE_MAX_EXPERTS:
         raise Unsupported(f"moe_group: {experts} experts ({MOE_MAX_EXPERTS} at most)")
-    _check(_fn("moe", "dl_moe_group")(_p(ids), pairs, experts, _p(place_of), _p(pair_at), _p(tiles), _p(n_tiles), _stream()),
-           "moe_group")
+    _check(_fn("moe", "dl_moe_group")(_p(ids), pairs, experts, _p(place_of), _p(pair_at), _p(tiles), _p(n_tiles), tile_rows,
+                                      _stream()), "moe_group")
 
 
 def moe_linear(a: torch.Tensor, pair_at: Optional[torch.Tensor], top_div: int, w: torch.Tensor, c: torch.Tensor,
-               tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, act: str = "none") -> None:
+               tiles: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, act: str = "none",
+               tile_rows: int = MOE_TILE_ROWS) -> None:
     """c[place] = act(a[row of place] w[expert of place]^T) for every place of every tile: w [experts, N, K], a rows of K
     numbers (the row of a place is pair_at[place] // top_div, or the place itself when pair_at is None), c [places, N]
     of a's dtype or float32. act: "none" or "relu2"."""
@@ -2028,7 +2046,8 @@ def moe_linear(a: torch.Tensor, pair_at: Optional[torch.Tensor], top_div: int, w
         raise InvalidArgument("moe_linear: w [experts, N, K] of a's dtype, a [rows, K], c [places, N] of a's dtype or float32")
     _check(_fn("moe", "dl_moe_linear")(dtype_code(a.dtype), dtype_code(c.dtype), _p(a), a.stride(0), _p(pair_at), top_div,
                                        _p(w), w.shape[1], w.shape[2], _p(c), c.stride(0), _p(tiles), _p(n_tiles), max_tiles,
-                                       1 if act == "relu2" else 0, 1 if MOE_TENSOR_CORES else 0, _stream()), "moe_linear")
+                                       1 if act == "relu2" else 0, 1 if MOE_TENSOR_CORES else 0, tile_rows, _stream()),
+           "moe_linear")
 
 
 def moe_combine(c: torch.Tensor, place_of: torch.Tensor, weights: torch.Tensor, top: int, y: torch.Tensor) -> None:

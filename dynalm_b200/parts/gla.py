@@ -83,10 +83,16 @@ class GatedLinearAttention:
         linear(x, self.w_in, proj)
         gate_col = 2 * self.qk + self.inner
         z = rt.buffer("gla_decay", (rows, self.qk), torch.float32)
-        ops.gemm_simt(proj[:, gate_col + self.inner:], self.w_decay, z, self.b_decay, 1.0)     # float32 out, with the bias
+        inner_vec = proj[:, gate_col + self.inner:]
+        if x.dtype == torch.float32:
+            ops.gemm_simt(inner_vec, self.w_decay, z, self.b_decay, 1.0)
+            z_bias = None
+        else:
+            linear(inner_vec, self.w_decay, z)         # float32 sums; the bias joins where the decays are formed
+            z_bias = self.b_decay
         o = rt.buffer("gla_o", (rows, self.inner), torch.float32)
         ops.gla_scan(proj, 0, self.qk, 2 * self.qk, z, self.tau, self.q_scale, state, ctx.q_start, ctx.state_slots, o,
-                     ctx.num_requests, H, d, e)
+                     ctx.num_requests, H, d, e, z_bias=z_bias)
         g = rt.buffer("gla_gated", (rows, self.inner))
         ops.head_norm_gate(o, proj, gate_col, self.norm, self.eps, g, H, e)
         return linear_partial(g, self.w_o, rt, self.out_name)

@@ -22,7 +22,7 @@ from typing import Dict
 import torch
 
 from ..errors import Unsupported
-from ..kernels import ops
+from ..kernels import linear, ops
 from .base import TensorDecl, register_feed_forward
 
 
@@ -63,7 +63,7 @@ class RoutedMLP:
         E, top = self.E, self.top
         pairs = rows * top
         logits = rt.buffer("moe_logits", (rows, E), torch.float32)
-        ops.gemm_simt(x, self.w_router, logits, None, 1.0)                # float32 accumulation and result
+        linear(x, self.w_router, logits)                                  # float32 accumulation and result
         ids = rt.buffer("moe_ids", (rows, top), torch.int32)
         weights = rt.buffer("moe_weights", (rows, top), torch.float32)
         ops.moe_route(logits, top, self.groups, self.keep, self.scale, ids, weights)
@@ -72,12 +72,13 @@ class RoutedMLP:
         pair_at = rt.flat(f"moe_pair_at_{top}", most, torch.int32)
         tiles = rt.flat(f"moe_tiles_{top}_{E}", 3 * ops.moe_max_tiles(most, E), torch.int32)
         n_tiles = rt.flat("moe_n_tiles", 1, torch.int32)
-        ops.moe_group(ids, pairs, E, place_of, pair_at, tiles, n_tiles)
-        max_tiles = ops.moe_max_tiles(pairs, E)
+        tile_rows = ops.moe_tile_rows(pairs, E, x, (s.width, s.inner))
+        ops.moe_group(ids, pairs, E, place_of, pair_at, tiles, n_tiles, tile_rows)
+        max_tiles = ops.moe_max_tiles(pairs, E, tile_rows)
         act = rt.flat(f"moe_act_{top}_{s.inner}", most * s.inner, x.dtype)[:pairs * s.inner].view(pairs, s.inner)
-        ops.moe_linear(x, pair_at, top, self.w_up, act, tiles, n_tiles, max_tiles, "relu2")
+        ops.moe_linear(x, pair_at, top, self.w_up, act, tiles, n_tiles, max_tiles, "relu2", tile_rows)
         per_pair = rt.flat(f"moe_out_{top}_{s.width}", most * s.width, torch.float32)[:pairs * s.width].view(pairs, s.width)
-        ops.moe_linear(act, None, 1, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none")
+        ops.moe_linear(act, None, 1, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none", tile_rows)
         y = rt.buffer("ffn_out", (rows, s.width))
         ops.moe_combine(per_pair, place_of, weights, top, y)
         return y

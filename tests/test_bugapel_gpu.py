@@ -410,33 +410,36 @@ def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
         ids[ids == E - 1] = 0                          # the last expert idles
     weights = rng.rand(rows, top) + 0.1
     pairs = rows * top
-    place_of = torch.zeros(pairs, dtype=torch.int32, device=DEV)
-    pair_at = torch.zeros(pairs, dtype=torch.int32, device=DEV)
-    max_tiles = ops.moe_max_tiles(pairs, E)
-    tiles = torch.zeros(3 * max_tiles, dtype=torch.int32, device=DEV)
-    n_tiles = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.moe_group(_ints(ids.reshape(-1)), pairs, E, place_of, pair_at, tiles, n_tiles)
-    po, pa = place_of.cpu().numpy(), pair_at.cpu().numpy()
-    assert sorted(po) == list(range(pairs)) and all(pa[po[p]] == p for p in range(pairs))
-    by_place = ids.reshape(-1)[pa]
-    assert all(by_place[i] <= by_place[i + 1] for i in range(pairs - 1)), "places run expert by expert"
-    nt = int(n_tiles[0])
-    covered = []
-    for ex, first, count in tiles[:3 * nt].view(nt, 3).cpu().numpy():
-        assert 0 < count <= ops.MOE_TILE_ROWS and all(by_place[first:first + count] == ex)
-        covered += list(range(first, first + count))
-    assert sorted(covered) == list(range(pairs))
-    act = torch.zeros(pairs, inner, dtype=dtype, device=DEV)
-    ops.moe_linear(_t(x, dtype), pair_at, top, _t(up, dtype), act, tiles, n_tiles, max_tiles, "relu2")
-    out = torch.zeros(pairs, width, device=DEV)
-    ops.moe_linear(act, None, 1, _t(down, dtype), out, tiles, n_tiles, max_tiles, "none")
-    y = torch.zeros(rows, width, dtype=dtype, device=DEV)
-    ops.moe_combine(out, place_of, _t(weights), top, y)
     want = np.zeros((rows, width))
     for r in range(rows):
         for k in range(top):
             want[r] += weights[r, k] * plain.expert(x[r], up[ids[r, k]], down[ids[r, k]])
-    _close(_np(y), want, 3e-5 if dtype == torch.float32 else 3e-2, "the experts' weighted sum")
+    wide = dtype == torch.bfloat16 and width % 32 == 0 and inner % 32 == 0
+    for tile_rows in ((ops.MOE_TILE_ROWS, ops.MOE_WIDE_TILE_ROWS) if wide else (ops.MOE_TILE_ROWS,)):
+        place_of = torch.zeros(pairs, dtype=torch.int32, device=DEV)
+        pair_at = torch.zeros(pairs, dtype=torch.int32, device=DEV)
+        max_tiles = ops.moe_max_tiles(pairs, E, tile_rows)
+        tiles = torch.zeros(3 * max_tiles, dtype=torch.int32, device=DEV)
+        n_tiles = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.moe_group(_ints(ids.reshape(-1)), pairs, E, place_of, pair_at, tiles, n_tiles, tile_rows)
+        po, pa = place_of.cpu().numpy(), pair_at.cpu().numpy()
+        assert sorted(po) == list(range(pairs)) and all(pa[po[p]] == p for p in range(pairs))
+        by_place = ids.reshape(-1)[pa]
+        assert all(by_place[i] <= by_place[i + 1] for i in range(pairs - 1)), "places run expert by expert"
+        nt = int(n_tiles[0])
+        assert nt <= max_tiles
+        covered = []
+        for ex, first, count in tiles[:3 * nt].view(nt, 3).cpu().numpy():
+            assert 0 < count <= tile_rows and all(by_place[first:first + count] == ex)
+            covered += list(range(first, first + count))
+        assert sorted(covered) == list(range(pairs))
+        act = torch.zeros(pairs, inner, dtype=dtype, device=DEV)
+        ops.moe_linear(_t(x, dtype), pair_at, top, _t(up, dtype), act, tiles, n_tiles, max_tiles, "relu2", tile_rows)
+        out = torch.zeros(pairs, width, device=DEV)
+        ops.moe_linear(act, None, 1, _t(down, dtype), out, tiles, n_tiles, max_tiles, "none", tile_rows)
+        y = torch.zeros(rows, width, dtype=dtype, device=DEV)
+        ops.moe_combine(out, place_of, _t(weights), top, y)
+        _close(_np(y), want, 3e-5 if dtype == torch.float32 else 3e-2, f"the experts' weighted sum, tiles of {tile_rows}")
 
 
 # ---------------------------------------------------------------------------------------------
