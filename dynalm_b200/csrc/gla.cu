@@ -21,7 +21,10 @@ namespace dl {
 
 constexpr int GLA_TILE = 16;
 
-template <typename T, int R>
+// PRE: the next tile's numbers are asked for before the current tile is computed and wait in registers meanwhile (at most
+// 8 of q, k and the decays each and 2 values a thread: Dp <= 128 with 256 threads), so that a tile's trip to memory hides
+// behind the arithmetic of the tile in front of it.
+template <typename T, int R, bool PRE>
 __global__ void __launch_bounds__(256)
 gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, int v_col, const float* __restrict__ alpha,
                 int a_stride, float q_scale, float* __restrict__ state, size_t state_stride,
@@ -51,27 +54,72 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
     S[j] = (live && i < d) ? srow[i] : 0.0f;
   }
 
+  constexpr int MAXF = 8, MAXV = 2;
+  // as they lie in memory: nothing here may depend on a number that is still on its way, or the warp would wait for it
+  T pq[PRE ? MAXF : 1], pk[PRE ? MAXF : 1], pv[PRE ? MAXV : 1];
+  float pa[PRE ? MAXF : 1];
+  auto fetch = [&](int t0, int nt) {                // PRE only: a tile's numbers into registers
+    int t = tid / Dp, i = tid % Dp;
+    const int dt = 256 / Dp, di = 256 % Dp;
+#pragma unroll
+    for (int c = 0; c < MAXF; ++c) {
+      pq[c] = pk[c] = from_float<T>(0.0f);
+      pa[c] = 0.0f;
+      if (t < nt && i < d) {
+        const T* prow = proj + static_cast<size_t>(t0 + t) * stride;
+        pq[c] = prow[q_col + head * d + i];
+        pk[c] = prow[k_col + head * d + i];
+        pa[c] = alpha[static_cast<size_t>(t0 + t) * a_stride + head * d + i];
+      }
+      t += dt;
+      i += di;
+      if (i >= Dp) { i -= Dp; ++t; }
+    }
+#pragma unroll
+    for (int c = 0; c < MAXV; ++c) {
+      const int x = tid + 256 * c, tt = x / cols, cc = x % cols;
+      pv[c] = from_float<T>(0.0f);
+      if (tt < nt && c0 + cc < e) pv[c] = proj[static_cast<size_t>(t0 + tt) * stride + v_col + head * e + c0 + cc];
+    }
+  };
+  if (PRE) fetch(r0, min(GLA_TILE, r1 - r0));
+
   for (int t0 = r0; t0 < r1; t0 += GLA_TILE) {
     const int nt = min(GLA_TILE, r1 - t0);
     __syncthreads();                              // the tile before has been read
-    for (int x = tid; x < nt * Dp; x += nthr) {
-      const int t = x / Dp, i = x % Dp;
-      float qv = 0.0f, kv = 0.0f, av = 0.0f;
-      if (i < d) {
-        const T* prow = proj + static_cast<size_t>(t0 + t) * stride;
-        qv = to_float(prow[q_col + head * d + i]) * q_scale;
-        kv = to_float(prow[k_col + head * d + i]);
-        av = alpha[static_cast<size_t>(t0 + t) * a_stride + head * d + i];
+    if (PRE) {
+#pragma unroll
+      for (int c = 0; c < MAXF; ++c) {
+        const int x = tid + 256 * c;
+        if (x < GLA_TILE * Dp) { s_q[x] = to_float(pq[c]) * q_scale; s_k[x] = to_float(pk[c]); s_a[x] = pa[c]; }
       }
-      s_q[x] = qv;
-      s_k[x] = kv;
-      s_a[x] = av;
+#pragma unroll
+      for (int c = 0; c < MAXV; ++c) {
+        const int x = tid + 256 * c;
+        if (x < GLA_TILE * cols) s_v[x] = to_float(pv[c]);
+      }
+      __syncthreads();
+      if (t0 + GLA_TILE < r1) fetch(t0 + GLA_TILE, min(GLA_TILE, r1 - t0 - GLA_TILE));
+    } else {
+      for (int x = tid; x < nt * Dp; x += nthr) {
+        const int t = x / Dp, i = x % Dp;
+        float qv = 0.0f, kv = 0.0f, av = 0.0f;
+        if (i < d) {
+          const T* prow = proj + static_cast<size_t>(t0 + t) * stride;
+          qv = to_float(prow[q_col + head * d + i]) * q_scale;
+          kv = to_float(prow[k_col + head * d + i]);
+          av = alpha[static_cast<size_t>(t0 + t) * a_stride + head * d + i];
+        }
+        s_q[x] = qv;
+        s_k[x] = kv;
+        s_a[x] = av;
+      }
+      for (int x = tid; x < nt * cols; x += nthr) {
+        const int t = x / cols, c = x % cols;
+        s_v[x] = c0 + c < e ? to_float(proj[static_cast<size_t>(t0 + t) * stride + v_col + head * e + c0 + c]) : 0.0f;
+      }
+      __syncthreads();
     }
-    for (int x = tid; x < nt * cols; x += nthr) {
-      const int t = x / cols, c = x % cols;
-      s_v[x] = c0 + c < e ? to_float(proj[static_cast<size_t>(t0 + t) * stride + v_col + head * e + c0 + c]) : 0.0f;
-    }
-    __syncthreads();
     if ((tid & ~31) / P < cols) {                 // warps that hold columns; all their lanes walk the tile (the shuffles
       const int clr = cl < cols ? cl : cols - 1;  // name the whole warp), the other warps of the block only fetch
       for (int t = 0; t < nt; ++t) {
@@ -148,6 +196,10 @@ DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, in
     return DL_ERR_UNSUPPORTED;
   int P = 1;
   while (P * 16 < d) P <<= 1;                      // lanes a column: the fewest that leave a lane at most 16 rows
+  // A warp walks its tokens one after the other, each a short chain of dependent instructions, so what fills an SM is the
+  // number of warps: while the step has fewer than eight computing warps an SM (one long prompt), a column is laid over
+  // more lanes (down to four rows a lane), which costs a shuffle a doubling.
+  while (P < 32 && d >= 8 * P && static_cast<long long>(requests) * H * e * P / 32 < 8ll * sm_count) P <<= 1;
   const int R = ((d + P - 1) / P + 3) / 4 * 4;     // rows a lane, in fours
   int cols = 256 / P;                              // columns a block of 256 threads takes
   if (cols > e) cols = e;
@@ -159,10 +211,16 @@ DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, in
   const int Dp = P * R;
   const size_t smem = static_cast<size_t>(dl::GLA_TILE) * (3 * Dp + 2 * cols) * sizeof(float);
   dim3 grid((e + cols - 1) / cols, H, requests);
+  const bool pre = Dp <= 128 && cols <= 32;
 #define DL_GLA(T, RR)                                                                                                    \
   do {                                                                                                                   \
-    cudaFuncSetAttribute(dl::gla_scan_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    dl::gla_scan_kernel<T, RR><<<grid, threads, smem, stream>>>(static_cast<const T*>(proj), stride, q_col, k_col, v_col, alpha, \
+    if (pre) DL_GLA_P(T, RR, true);                                                                                      \
+    else DL_GLA_P(T, RR, false);                                                                                         \
+  } while (0)
+#define DL_GLA_P(T, RR, PP)                                                                                              \
+  do {                                                                                                                   \
+    cudaFuncSetAttribute(dl::gla_scan_kernel<T, RR, PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::gla_scan_kernel<T, RR, PP><<<grid, threads, smem, stream>>>(static_cast<const T*>(proj), stride, q_col, k_col, v_col, alpha, \
                                                                 a_stride, q_scale, state,                                \
                                                                 static_cast<size_t>(state_stride), q_start, state_slots, o, \
                                                                 H, d, e, P, cols);                                       \
@@ -178,5 +236,6 @@ DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, in
   else DL_GLA_R(dl::bf16);
 #undef DL_GLA_R
 #undef DL_GLA
+#undef DL_GLA_P
   return dl::launch_status();
 }

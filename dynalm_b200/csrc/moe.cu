@@ -177,98 +177,19 @@ moe_linear_simt_kernel(const T* __restrict__ a, int lda, const int* __restrict__
   }
 }
 
-// bfloat16 on the tensor cores: tile = 32 places x 128 features, 8 warps, warp w takes features 16 w .. 16 w + 15 of the
-// tile for all 32 places (two m16 x two n8 fragments), k in steps of 32 through shared memory (rows padded to 40
-// numbers, so that the fragment loads of a warp fall on different banks).
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <typename TO>
-__global__ void __launch_bounds__(256)
-moe_linear_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
-                      const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
-                      const int* __restrict__ n_tiles, int act) {
-  constexpr int TN = 128, TK = 32, LD = TK + 8;
-  __shared__ __align__(16) bf16 As[2][MOE_TM][LD];
-  __shared__ __align__(16) bf16 Bs[2][TN][LD];
-  __shared__ int src[MOE_TM];
-  if (static_cast<int>(blockIdx.y) >= n_tiles[0]) return;
-  const int* tl = tiles + 3 * blockIdx.y;
-  const int ex = tl[0], p0 = tl[1], np = tl[2];
-  const int n0 = blockIdx.x * TN;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid < MOE_TM) src[tid] = tid < np ? (pair_at != nullptr ? pair_at[p0 + tid] / top_div : p0 + tid) : -1;
-  __syncthreads();
-  const bf16* wx = w + static_cast<size_t>(ex) * N * K;
-  float acc[2][2][4] = {};
-  // a stage: A 32 x 32 numbers = 128 pieces of 16 bytes (threads 0..127), B 128 x 32 = 512 pieces (2 a thread)
-  auto load = [&](int stage, int k0) {
-    if (tid < 128) {
-      const int r = tid >> 2, piece = tid & 3;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (src[r] >= 0) v = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(src[r]) * lda + k0 + piece * 8);
-      *reinterpret_cast<uint4*>(&As[stage][r][piece * 8]) = v;
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int x = tid + 256 * i, n = x >> 2, piece = x & 3;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (n0 + n < N) v = *reinterpret_cast<const uint4*>(wx + static_cast<size_t>(n0 + n) * K + k0 + piece * 8);
-      *reinterpret_cast<uint4*>(&Bs[stage][n][piece * 8]) = v;
-    }
-  };
-  const int steps = K / TK;
-  load(0, 0);
-  __syncthreads();
-  const int g = lane >> 2, q = lane & 3;
-  for (int s = 0; s < steps; ++s) {
-    const int st = s & 1;
-    if (s + 1 < steps) load(st ^ 1, (s + 1) * TK);
-#pragma unroll
-    for (int kk = 0; kk < TK; kk += 16) {
-      uint32_t af[2][4], bfr[2][2];
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi) {
-        const bf16* base = &As[st][mi * 16][0];
-        af[mi][0] = *reinterpret_cast<const uint32_t*>(base + g * LD + kk + q * 2);
-        af[mi][1] = *reinterpret_cast<const uint32_t*>(base + (g + 8) * LD + kk + q * 2);
-        af[mi][2] = *reinterpret_cast<const uint32_t*>(base + g * LD + kk + 8 + q * 2);
-        af[mi][3] = *reinterpret_cast<const uint32_t*>(base + (g + 8) * LD + kk + 8 + q * 2);
-      }
-#pragma unroll
-      for (int ni = 0; ni < 2; ++ni) {
-        const bf16* base = &Bs[st][warp * 16 + ni * 8 + g][0];
-        bfr[ni][0] = *reinterpret_cast<const uint32_t*>(base + kk + q * 2);
-        bfr[ni][1] = *reinterpret_cast<const uint32_t*>(base + kk + 8 + q * 2);
-      }
-#pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-        for (int ni = 0; ni < 2; ++ni) mma_bf16_16816(acc[mi][ni], af[mi], bfr[ni]);
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-    for (int ni = 0; ni < 2; ++ni)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = mi * 16 + g + 8 * h;
-        const int n = n0 + warp * 16 + ni * 8 + q * 2;
-        if (r >= np) continue;
-        TO* dst = c + static_cast<size_t>(p0 + r) * ldc + n;
-        if (n < N) dst[0] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h], act));
-        if (n + 1 < N) dst[1] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h + 1], act));
-      }
-}
-
-// bfloat16 on the tensor cores for many places an expert: tile = 128 places x 128 features, 8 warps as 2 x 4 (a warp
-// takes 64 places x 32 features: four m16 by four n8 fragments), k in steps of 32 through a cp.async double buffer,
-// fragments by ldmatrix. The matrix of the tile's expert is read once per 128 places instead of once per 32.
+// bfloat16 on the tensor cores: tile = TM places x 128 features, 8 warps as WM x (8 / WM), k in steps of BK through a
+// cp.async double buffer (the next step's A and W are on their way while this one is multiplied), fragments by
+// ldmatrix, rows padded by 16 bytes so that a fragment's rows fall on different banks.
+//   TM = 128, WM = 2, BK = 32: a warp takes 64 places x 32 features; for steps that bring an expert many places, whose
+//   matrix is then read once per 128 places.
+//   TM = 32, WM = 1, BK = 64: a warp takes all 32 places x 16 features; for steps that bring an expert a few places (a
+//   decode batch), which stream every touched expert's matrix once and are bound by that stream.
 __device__ __forceinline__ void moe_cp16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
@@ -280,12 +201,15 @@ __device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* sm
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
-template <typename TO>
+template <int TM, int WM, int BK, typename TO>
 __global__ void __launch_bounds__(256)
-moe_linear_wide_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
-                       const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
-                       const int* __restrict__ n_tiles, int act) {
-  constexpr int TM = MOE_TM_WIDE, TN = 128, TK = 32, LD = TK + 8;
+moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
+                     const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
+                     const int* __restrict__ n_tiles, int act) {
+  constexpr int TN = 128, LD = BK + 8, WN = 8 / WM;
+  constexpr int MI = TM / WM / 16;          // m16 fragments a warp
+  constexpr int NI = TN / WN / 8;           // n8 fragments a warp (two per ldmatrix.x4)
+  constexpr int CH = BK / 8;                // 16-byte pieces a row of a stage
   __shared__ __align__(16) bf16 As[2][TM][LD];
   __shared__ __align__(16) bf16 Bs[2][TN][LD];
   __shared__ int src[TM];
@@ -294,47 +218,48 @@ moe_linear_wide_kernel(const bf16* __restrict__ a, int lda, const int* __restric
   const int ex = tl[0], p0 = tl[1], np = tl[2];
   const int n0 = blockIdx.x * TN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wm = warp >> 2, wn = warp & 3;               // the warp's 64 places and 32 features
+  const int wm = warp / WN, wn = warp % WN;
   if (tid < TM) src[tid] = tid < np ? (pair_at != nullptr ? pair_at[p0 + tid] / top_div : p0 + tid) : -1;
   __syncthreads();
   const bf16* wx = w + static_cast<size_t>(ex) * N * K;
-  // a stage: A and B 128 x 32 numbers = 512 pieces of 16 bytes each, two a thread
   auto load = [&](int stage, int k0) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int x = tid + 256 * i, r = x >> 2, piece = x & 3;
+    for (int x = tid; x < TM * CH; x += 256) {
+      const int r = x / CH, piece = x % CH;
       const bool ok = src[r] >= 0;
       moe_cp16(&As[stage][r][piece * 8], a + static_cast<size_t>(ok ? src[r] : 0) * lda + k0 + piece * 8, ok);
-      const bool okb = n0 + r < N;
-      moe_cp16(&Bs[stage][r][piece * 8], wx + static_cast<size_t>(okb ? n0 + r : 0) * K + k0 + piece * 8, okb);
+    }
+    for (int x = tid; x < TN * CH; x += 256) {
+      const int r = x / CH, piece = x % CH;
+      const bool ok = n0 + r < N;
+      moe_cp16(&Bs[stage][r][piece * 8], wx + static_cast<size_t>(ok ? n0 + r : 0) * K + k0 + piece * 8, ok);
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
-  float acc[4][4][4] = {};
-  const int steps = K / TK;
+  float acc[MI][NI][4] = {};
+  const int steps = K / BK;
   load(0, 0);
   for (int s = 0; s < steps; ++s) {
     const int st = s & 1;
     if (s + 1 < steps) {
-      load(st ^ 1, (s + 1) * TK);
+      load(st ^ 1, (s + 1) * BK);
       asm volatile("cp.async.wait_group 1;\n" ::);
     } else {
       asm volatile("cp.async.wait_group 0;\n" ::);
     }
     __syncthreads();
 #pragma unroll
-    for (int kk = 0; kk < TK; kk += 16) {
-      uint32_t af[4][4], bfr[2][4];
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[MI][4], bfr[NI / 2][4];
 #pragma unroll
-      for (int mi = 0; mi < 4; ++mi)
-        moe_ldmatrix_x4(af[mi], &As[st][wm * 64 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
+      for (int mi = 0; mi < MI; ++mi)
+        moe_ldmatrix_x4(af[mi], &As[st][wm * (TM / WM) + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
 #pragma unroll
-      for (int nj = 0; nj < 2; ++nj)       // two n8 fragments per ldmatrix.x4
-        moe_ldmatrix_x4(bfr[nj], &Bs[st][wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+      for (int nj = 0; nj < NI / 2; ++nj)       // two n8 fragments per ldmatrix.x4
+        moe_ldmatrix_x4(bfr[nj], &Bs[st][wn * (TN / WN) + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
-      for (int mi = 0; mi < 4; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
+        for (int ni = 0; ni < NI; ++ni) {
           const uint32_t b2[2] = {bfr[ni >> 1][(ni & 1) * 2], bfr[ni >> 1][(ni & 1) * 2 + 1]};
           mma_bf16_16816(acc[mi][ni], af[mi], b2);
         }
@@ -343,13 +268,13 @@ moe_linear_wide_kernel(const bf16* __restrict__ a, int lda, const int* __restric
   }
   const int g = lane >> 2, q = lane & 3;
 #pragma unroll
-  for (int mi = 0; mi < 4; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni)
+    for (int ni = 0; ni < NI; ++ni)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int r = wm * 64 + mi * 16 + g + 8 * h;
-        const int n = n0 + wn * 32 + ni * 8 + q * 2;
+        const int r = wm * (TM / WM) + mi * 16 + g + 8 * h;
+        const int n = n0 + wn * (TN / WN) + ni * 8 + q * 2;
         if (r >= np) continue;
         TO* dst = c + static_cast<size_t>(p0 + r) * ldc + n;
         if (n < N) dst[0] = from_float<TO>(apply_act<bf16>(acc[mi][ni][2 * h], act));
@@ -392,41 +317,35 @@ DL_EXPORT int dl_moe_group(const int* ids, int pairs, int E, int* place_of, int*
 
 // dtype of a and w: 0 float32, 1 bfloat16; out_dtype of c likewise. pair_at null: the rows of a are the places
 // themselves; else the row of a place is pair_at[place] / top_div. act: 0 none, 1 squared ReLU. tensor_cores: use the
-// mma.sync kernel where it applies (bfloat16, K a multiple of 32, rows of a and w on 16-byte boundaries).
+// mma.sync kernels where they apply (bfloat16, K a multiple of 64, rows of a and w on 16-byte boundaries).
 // tile_rows: the places a tile as dl_moe_group was told: 32, or 128 for the wide tensor-core kernel (bfloat16 only).
 DL_EXPORT int dl_moe_linear(int dtype, int out_dtype, const void* a, int lda, const int* pair_at, int top_div, const void* w,
                             int N, int K, void* c, int ldc, const int* tiles, const int* n_tiles, int max_tiles, int act,
                             int tensor_cores, int tile_rows, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N <= 0 || K <= 0 || top_div <= 0 || max_tiles > 65535) return DL_ERR_UNSUPPORTED;
-  const bool tc_ok = dtype == 1 && tensor_cores && K % 32 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+  const bool wide = tile_rows == dl::MOE_TM_WIDE;
+  if (!wide && tile_rows != dl::MOE_TM) return DL_ERR_UNSUPPORTED;
+  const bool tc_ok = dtype == 1 && tensor_cores && K % 64 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-  if (tile_rows == dl::MOE_TM_WIDE) {
-    if (!tc_ok) return DL_ERR_UNSUPPORTED;
-    dim3 grid((N + 127) / 128, max_tiles);
-    if (out_dtype == 1)
-      dl::moe_linear_wide_kernel<dl::bf16><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
-                                                                      static_cast<const dl::bf16*>(w), N, K,
-                                                                      static_cast<dl::bf16*>(c), ldc, tiles, n_tiles, act);
-    else if (out_dtype == 0)
-      dl::moe_linear_wide_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
-                                                                   static_cast<const dl::bf16*>(w), N, K, static_cast<float*>(c),
-                                                                   ldc, tiles, n_tiles, act);
-    else return DL_ERR_UNSUPPORTED;
-    return dl::launch_status();
-  }
-  if (tile_rows != dl::MOE_TM) return DL_ERR_UNSUPPORTED;
+  if (wide && !tc_ok) return DL_ERR_UNSUPPORTED;
   if (tc_ok) {
     dim3 grid((N + 127) / 128, max_tiles);
-    if (out_dtype == 1)
-      dl::moe_linear_mma_kernel<dl::bf16><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
-                                                                     static_cast<const dl::bf16*>(w), N, K,
-                                                                     static_cast<dl::bf16*>(c), ldc, tiles, n_tiles, act);
-    else if (out_dtype == 0)
-      dl::moe_linear_mma_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const dl::bf16*>(a), lda, pair_at, top_div,
-                                                                  static_cast<const dl::bf16*>(w), N, K, static_cast<float*>(c),
-                                                                  ldc, tiles, n_tiles, act);
+#define DL_MOE_TC(TO)                                                                                                     \
+  do {                                                                                                                    \
+    if (wide)                                                                                                             \
+      dl::moe_linear_tc_kernel<dl::MOE_TM_WIDE, 2, 32, TO><<<grid, 256, 0, stream>>>(                                     \
+          static_cast<const dl::bf16*>(a), lda, pair_at, top_div, static_cast<const dl::bf16*>(w), N, K, static_cast<TO*>(c), \
+          ldc, tiles, n_tiles, act);                                                                                      \
+    else                                                                                                                  \
+      dl::moe_linear_tc_kernel<dl::MOE_TM, 1, 64, TO><<<grid, 256, 0, stream>>>(                                          \
+          static_cast<const dl::bf16*>(a), lda, pair_at, top_div, static_cast<const dl::bf16*>(w), N, K, static_cast<TO*>(c), \
+          ldc, tiles, n_tiles, act);                                                                                      \
+  } while (0)
+    if (out_dtype == 1) DL_MOE_TC(dl::bf16);
+    else if (out_dtype == 0) DL_MOE_TC(float);
     else return DL_ERR_UNSUPPORTED;
+#undef DL_MOE_TC
     return dl::launch_status();
   }
   dim3 grid((N + 63) / 64, max_tiles);

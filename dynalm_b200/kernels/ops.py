@@ -1993,8 +1993,8 @@ def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> i
 
 def moe_tile_rows(pairs: int, experts: int, a: torch.Tensor, widths) -> int:
     """Places a tile for a step of `pairs` pairs: 128 where the wide tensor-core kernel applies (bfloat16, every inner
-    size in `widths` a multiple of 32) and an expert gets enough places on average, else 32."""
-    wide = (MOE_TENSOR_CORES and a.dtype == torch.bfloat16 and all(w % 32 == 0 for w in widths)
+    size in `widths` a multiple of 64) and an expert gets enough places on average, else 32."""
+    wide = (MOE_TENSOR_CORES and a.dtype == torch.bfloat16 and all(w % 64 == 0 for w in widths)
             and pairs >= MOE_WIDE_FROM * experts)
     return MOE_WIDE_TILE_ROWS if wide else MOE_TILE_ROWS
 

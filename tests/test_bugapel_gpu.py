@@ -348,6 +348,30 @@ def test_linear_attention_in_portions_keeps_its_state(dtype, H, d, e, tau):
     _close(_np(o), _gla_plain(u, z, H, d, e, tau)[0], tol, "a slot used again")
 
 
+@pytest.mark.parametrize("H,d,e", [(8, 64, 128), (4, 128, 96)])
+def test_linear_attention_of_many_requests_side_by_side(H, d, e):
+    """A dozen requests in one step (single tokens, then two or three tokens each): with that many columns in flight the
+    kernel lays a column over the fewest lanes, the layout a large decode batch runs with."""
+    from dynalm_b200.kernels import ops
+    rng = np.random.RandomState(d + e)
+    n_req, tau = 24, 4.0
+    seqs = [_gla_inputs(rng, 7, H, d, e, torch.float32) for _ in range(n_req)]
+    want = [_gla_plain(u, z, H, d, e, tau)[0] for u, z in seqs]
+    state = torch.zeros(n_req + 1, H * d * e, device=DEV)
+    slots = [(5 * r) % n_req for r in range(n_req)]
+    at = 0
+    for take in (1, 1, 3, 2):
+        proj = torch.cat([_t(u[at:at + take]) for u, _ in seqs])
+        z = torch.cat([_t(zz[at:at + take]) for _, zz in seqs]).contiguous()
+        o = torch.zeros(n_req * take, H * e, device=DEV)
+        ops.gla_scan(proj, 0, H * d, 2 * H * d, z, tau, d ** -0.5, state, _ints(range(0, n_req * take + 1, take)), _ints(slots), o,
+                     n_req, H, d, e)
+        for r in range(n_req):
+            _close(_np(o[r * take:(r + 1) * take]), want[r][at:at + take], 3e-5, f"request {r}, tokens from {at}")
+        at += take
+    assert (state[n_req] == 0).all()
+
+
 def test_linear_attention_reads_after_the_write_and_decays_rows():
     """One token from an empty state: o = (q . k) d^(-1/2) v, which a read before the write would leave at zero. A
     second token with k = 0: the state's row of key channel i has decayed by sigmoid(z_i)^(1/tau), whatever the value
@@ -395,7 +419,7 @@ def test_router_picks_experts_of_the_best_groups(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,width,inner,rows", [(6, 2, 96, 40, 50), (4, 1, 64, 32, 7), (5, 5, 72, 17, 33), (8, 4, 256, 96, 300),
+@pytest.mark.parametrize("E,top,width,inner,rows", [(6, 2, 96, 40, 50), (4, 1, 64, 32, 7), (5, 5, 72, 17, 33), (8, 4, 256, 128, 300),
                                                     (3, 2, 128, 64, 1), (16, 2, 160, 224, 130)])
 def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
     """The whole feed-forward after the router: pairs grouped by expert (some experts get none, one gets more than a
@@ -414,7 +438,7 @@ def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
     for r in range(rows):
         for k in range(top):
             want[r] += weights[r, k] * plain.expert(x[r], up[ids[r, k]], down[ids[r, k]])
-    wide = dtype == torch.bfloat16 and width % 32 == 0 and inner % 32 == 0
+    wide = dtype == torch.bfloat16 and width % 64 == 0 and inner % 64 == 0
     for tile_rows in ((ops.MOE_TILE_ROWS, ops.MOE_WIDE_TILE_ROWS) if wide else (ops.MOE_TILE_ROWS,)):
         place_of = torch.zeros(pairs, dtype=torch.int32, device=DEV)
         pair_at = torch.zeros(pairs, dtype=torch.int32, device=DEV)
