@@ -184,11 +184,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 }
 
 // bfloat16 on the tensor cores: tile = TM places x 128 features, 8 warps as WM x (8 / WM), k in steps of BK through a
-// cp.async double buffer (the next step's A and W are on their way while this one is multiplied), fragments by
-// ldmatrix, rows padded by 16 bytes so that a fragment's rows fall on different banks.
-//   TM = 128, WM = 2, BK = 32: a warp takes 64 places x 32 features; for steps that bring an expert many places, whose
+// ring of STAGES cp.async buffers (the next steps' A and W are on their way while this one is multiplied, one block
+// barrier a step), fragments by ldmatrix, rows padded by 16 bytes so that a fragment's rows fall on different banks.
+//   TM = 128, WM = 2: a warp takes 64 places x 32 features; for steps that bring an expert many places, whose
 //   matrix is then read once per 128 places.
-//   TM = 32, WM = 1, BK = 64: a warp takes all 32 places x 16 features; for steps that bring an expert a few places (a
+//   TM = 32, WM = 1: a warp takes all 32 places x 16 features; for steps that bring an expert a few places (a
 //   decode batch), which stream every touched expert's matrix once and are bound by that stream.
 __device__ __forceinline__ void moe_cp16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -201,7 +201,7 @@ __device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* sm
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
-template <int TM, int WM, int BK, typename TO>
+template <int TM, int WM, int BK, int STAGES, typename TO>
 __global__ void __launch_bounds__(256)
 moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ pair_at, int top_div,
                      const bf16* __restrict__ w, int N, int K, TO* __restrict__ c, int ldc, const int* __restrict__ tiles,
@@ -210,8 +210,9 @@ moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict_
   constexpr int MI = TM / WM / 16;          // m16 fragments a warp
   constexpr int NI = TN / WN / 8;           // n8 fragments a warp (two per ldmatrix.x4)
   constexpr int CH = BK / 8;                // 16-byte pieces a row of a stage
-  __shared__ __align__(16) bf16 As[2][TM][LD];
-  __shared__ __align__(16) bf16 Bs[2][TN][LD];
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  bf16 (*As)[TM][LD] = reinterpret_cast<bf16 (*)[TM][LD]>(moe_smem);                                  // [STAGES][TM][LD]
+  bf16 (*Bs)[TN][LD] = reinterpret_cast<bf16 (*)[TN][LD]>(moe_smem + sizeof(bf16) * STAGES * TM * LD);  // [STAGES][TN][LD]
   __shared__ int src[TM];
   if (static_cast<int>(blockIdx.y) >= n_tiles[0]) return;
   const int* tl = tiles + 3 * blockIdx.y;
@@ -237,16 +238,18 @@ moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict_
   };
   float acc[MI][NI][4] = {};
   const int steps = K / BK;
-  load(0, 0);
+  // STAGES - 1 steps are on their way at any time; a group is committed every round (an empty one past the end), so that
+  // "all but the newest STAGES - 2 groups have landed" always names the step about to be multiplied
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i < steps) load(i, i * BK);
+    else asm volatile("cp.async.commit_group;\n" ::);
+  }
   for (int s = 0; s < steps; ++s) {
-    const int st = s & 1;
-    if (s + 1 < steps) {
-      load(st ^ 1, (s + 1) * BK);
-      asm volatile("cp.async.wait_group 1;\n" ::);
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::);
-    }
-    __syncthreads();
+    const int st = s % STAGES;
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+    __syncthreads();                         // step s is in shared memory, and every warp is done with step s - 1
+    if (s + STAGES - 1 < steps) load((s + STAGES - 1) % STAGES, (s + STAGES - 1) * BK);
+    else asm volatile("cp.async.commit_group;\n" ::);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[MI][4], bfr[NI / 2][4];
@@ -264,7 +267,6 @@ moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict_
           mma_bf16_16816(acc[mi][ni], af[mi], b2);
         }
     }
-    __syncthreads();
   }
   const int g = lane >> 2, q = lane & 3;
 #pragma unroll
@@ -331,21 +333,31 @@ DL_EXPORT int dl_moe_linear(int dtype, int out_dtype, const void* a, int lda, co
   if (wide && !tc_ok) return DL_ERR_UNSUPPORTED;
   if (tc_ok) {
     dim3 grid((N + 127) / 128, max_tiles);
-#define DL_MOE_TC(TO)                                                                                                     \
+#define DL_MOE_TC_ONE(TM_, WM_, BK_, TO)                                                                                  \
   do {                                                                                                                    \
-    if (wide)                                                                                                             \
-      dl::moe_linear_tc_kernel<dl::MOE_TM_WIDE, 2, 32, TO><<<grid, 256, 0, stream>>>(                                     \
-          static_cast<const dl::bf16*>(a), lda, pair_at, top_div, static_cast<const dl::bf16*>(w), N, K, static_cast<TO*>(c), \
-          ldc, tiles, n_tiles, act);                                                                                      \
-    else                                                                                                                  \
-      dl::moe_linear_tc_kernel<dl::MOE_TM, 1, 64, TO><<<grid, 256, 0, stream>>>(                                          \
-          static_cast<const dl::bf16*>(a), lda, pair_at, top_div, static_cast<const dl::bf16*>(w), N, K, static_cast<TO*>(c), \
-          ldc, tiles, n_tiles, act);                                                                                      \
+    constexpr int ST = 3;                                                                                                 \
+    constexpr int smem = ST * (TM_ + 128) * (BK_ + 8) * 2;                                                                \
+    static bool configured = false;                                                                                       \
+    if (!configured) {                                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(dl::moe_linear_tc_kernel<TM_, WM_, BK_, ST, TO>,                               \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                            \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                                   \
+      configured = true;                                                                                                  \
+    }                                                                                                                     \
+    dl::moe_linear_tc_kernel<TM_, WM_, BK_, ST, TO><<<grid, 256, smem, stream>>>(                                         \
+        static_cast<const dl::bf16*>(a), lda, pair_at, top_div, static_cast<const dl::bf16*>(w), N, K, static_cast<TO*>(c), \
+        ldc, tiles, n_tiles, act);                                                                                        \
+  } while (0)
+#define DL_MOE_TC(TO)                                         \
+  do {                                                        \
+    if (wide) DL_MOE_TC_ONE(dl::MOE_TM_WIDE, 2, 64, TO);      \
+    else DL_MOE_TC_ONE(dl::MOE_TM, 1, 64, TO);                \
   } while (0)
     if (out_dtype == 1) DL_MOE_TC(dl::bf16);
     else if (out_dtype == 0) DL_MOE_TC(float);
     else return DL_ERR_UNSUPPORTED;
 #undef DL_MOE_TC
+#undef DL_MOE_TC_ONE
     return dl::launch_status();
   }
   dim3 grid((N + 63) / 64, max_tiles);
