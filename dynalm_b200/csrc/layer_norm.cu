@@ -16,7 +16,8 @@
 namespace dl {
 
 constexpr int LN_THREADS = 256;
-constexpr int LN_MAX_PARTS = 8;
+constexpr int LN_MAX_PARTS = 16;      // the most parts a stream may have; a kernel instance holds 4, 8 or 16 of them (more
+                                      // than 8: one number at a time, or the parts would not fit the registers)
 
 // V numbers at a time: V = 4 when every row starts on a 16-byte boundary (W a multiple of 4), else 1.
 template <typename T, int V> struct LnVec {
@@ -51,7 +52,7 @@ template <int V> __device__ __forceinline__ void ln_store(bf16* p, const float* 
   }
 }
 
-template <typename TO, typename TD, int V>
+template <typename TO, typename TD, int V, int MAXP>
 __global__ void __launch_bounds__(LN_THREADS)
 stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float* __restrict__ init,
                          const TD* __restrict__ delta, int parts, size_t part_stride, float delta_scale,
@@ -74,17 +75,17 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
   const bool update = delta != nullptr;
   float sum = 0.0f;
   for (int c = tid * V; c < W; c += LN_THREADS * V) {
-    float x[LN_MAX_PARTS][V];
+    float x[MAXP][V];
     if (init != nullptr) {
       float v[V];
       LnVec<float, V>::load(init + static_cast<size_t>(row) * W + c, v);
 #pragma unroll
-      for (int s = 0; s < LN_MAX_PARTS; ++s)
+      for (int s = 0; s < MAXP; ++s)
 #pragma unroll
         for (int i = 0; i < V; ++i) x[s][i] = v[i];
     } else {
 #pragma unroll
-      for (int s = 0; s < LN_MAX_PARTS; ++s) {
+      for (int s = 0; s < MAXP; ++s) {
         if (s < S) {
           LnVec<float, V>::load(xrow + static_cast<size_t>(s) * W + c, x[s]);
         } else {
@@ -109,7 +110,7 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
 #pragma unroll
       for (int i = 0; i < V; ++i) y[i] *= delta_scale;
 #pragma unroll
-      for (int t = 0; t < LN_MAX_PARTS; ++t) {
+      for (int t = 0; t < MAXP; ++t) {
         if (t < S) {
           float v[V];
 #pragma unroll
@@ -117,7 +118,7 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
             float a = 0.0f;
             if (mix != nullptr) {
 #pragma unroll
-              for (int s = 0; s < LN_MAX_PARTS; ++s)
+              for (int s = 0; s < MAXP; ++s)
                 if (s < S) a = fmaf(s_mix[s * S + t], x[s][i], a);
             } else {
               a = x[t][i];
@@ -130,7 +131,7 @@ stream_layer_norm_kernel(float* __restrict__ streams, int S, int W, const float*
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < LN_MAX_PARTS; ++t) {
+      for (int t = 0; t < MAXP; ++t) {
         if (t < S) {
           if (init != nullptr && write_back) ln_store<V>(xrow + static_cast<size_t>(t) * W + c, x[t]);
 #pragma unroll
@@ -210,16 +211,16 @@ DL_EXPORT int dl_stream_layer_norm(int out_dtype, int delta_dtype, float* stream
   const bool wide = W % 4 == 0 && part_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(streams) | reinterpret_cast<uintptr_t>(init) |
                     reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b) |
                     reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+#define DL_LN_ONE(TO, TD, V, MAXP)                                                                                      \
+  dl::stream_layer_norm_kernel<TO, TD, V, MAXP><<<n_out, dl::LN_THREADS, smem, stream>>>(                               \
+      streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix,    \
+      outw, inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows)
 #define DL_LN(TO, TD)                                                                                                   \
   do {                                                                                                                  \
-    if (wide)                                                                                                           \
-      dl::stream_layer_norm_kernel<TO, TD, 4><<<n_out, dl::LN_THREADS, smem, stream>>>(                                 \
-          streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix, \
-          outw, inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows);                                           \
-    else                                                                                                                \
-      dl::stream_layer_norm_kernel<TO, TD, 1><<<n_out, dl::LN_THREADS, smem, stream>>>(                                 \
-          streams, S, W, init, static_cast<const TD*>(delta), parts, static_cast<size_t>(part_stride), delta_scale, mix, \
-          outw, inw, w, b, eps, static_cast<TO*>(out), rows_idx, total_rows);                                           \
+    if (wide && S <= 4) DL_LN_ONE(TO, TD, 4, 4);                                                                        \
+    else if (wide && S <= 8) DL_LN_ONE(TO, TD, 4, 8);                                                                   \
+    else if (S <= 4) DL_LN_ONE(TO, TD, 1, 4);                                                                           \
+    else DL_LN_ONE(TO, TD, 1, 16);                                                                                      \
   } while (0)
   if (out_dtype == 0 && delta_dtype == 0) DL_LN(float, float);
   else if (out_dtype == 1 && delta_dtype == 1) DL_LN(dl::bf16, dl::bf16);
@@ -227,6 +228,7 @@ DL_EXPORT int dl_stream_layer_norm(int out_dtype, int delta_dtype, float* stream
   else if (out_dtype == 0 && delta_dtype == 1) DL_LN(float, dl::bf16);
   else return DL_ERR_UNSUPPORTED;
 #undef DL_LN
+#undef DL_LN_ONE
   return dl::launch_status();
 }
 

@@ -1887,7 +1887,7 @@ def qk_rot_head_norm_cache(proj: torch.Tensor, inv_freq: Optional[torch.Tensor],
         proj.shape[0], heads, kv_heads, dim, vdim, page_size, _stream()), "qk_rot_head_norm_cache")
 
 
-STREAM_MAX_PARTS = 8       # the most parts a residual stream may have (csrc/layer_norm.cu)
+STREAM_MAX_PARTS = 16      # the most parts a residual stream may have (csrc/layer_norm.cu)
 
 
 def stream_layer_norm(streams: torch.Tensor, parts: int, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,

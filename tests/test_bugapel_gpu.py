@@ -82,7 +82,7 @@ def _close(got, want, tol, what=""):
 # ---------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("parts,width", [(1, 72), (3, 96), (4, 256), (8, 40), (2, 1001)])
+@pytest.mark.parametrize("parts,width", [(1, 72), (3, 96), (4, 256), (8, 40), (2, 1001), (13, 64), (16, 30), (5, 9)])
 def test_layer_norm_over_a_stream_of_parts(dtype, parts, width):
     """The first layer's copy of the embedding into every part, the update that a sublayer leaves (plain and as
     partial sums), the weighted read, the gather of wanted rows without a write, and a row with a large mean (the
