@@ -53,6 +53,16 @@ DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, in
   return t5_launch<dl::T5Alone>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, status, none, stream);
 }
 
+// A grouped product on the same kernel: runs of a's rows, listed on the device as row tiles (matrix, first row, rows <=
+// 128; n_tiles[0] of them, at most max_row_tiles), each run times its own matrix of w [matrices, N, K]. mode 0: y bf16,
+// 1: y fp32, 4: y bf16 = max(., 0)^2. The experts of a mixture-of-experts feed-forward (csrc/moe.cu writes the list).
+DL_EXPORT int dl_gemm_tcgen05_grouped(const void* a, int lda, int rows, const void* w, int matrices, int N, int K, void* y,
+                                      int ldy, int mode, const int* tiles, const int* n_tiles, int max_row_tiles, int* status,
+                                      cudaStream_t stream) {
+  return t5_launch_grouped<dl::T5Alone>(a, lda, rows, w, matrices, N, K, y, ldy, mode, tiles, n_tiles, max_row_tiles, status,
+                                        stream);
+}
+
 // The q | k | v projection with the rotary encoding and the cache write in the epilogue: w bf16 [(n_heads + 2
 // n_kv_heads) * head_dim, K], head_dim 64 or 128 with the whole head rotated; rotated q goes to q_out [M, ldq]
 // (16-byte aligned rows), rotated k and plain v to the caches [pages, page_size, n_kv_heads, head_dim]. angles:

@@ -58,11 +58,23 @@ __host__ __device__ __forceinline__ void t5_tile_coords(int tile, int tiles_n, i
 // from L2 once per pair (measured: the kernel is bound by operand traffic from L2; loading a third less made it
 // a fifth faster). A stage is then free only when both blocks' MMAs have read it: each block's commit arrives on
 // the stage's barrier in both blocks, and the barrier counts two arrivals.
+// A grouped product: the rows of x come in runs, each run multiplied by a matrix of its own (the experts of a mixture),
+// and which rows form a run is known on the device only. `tiles` lists row tiles as (matrix, first row, rows <= 128),
+// `n_tiles[0]` says how many; matrix g lies w_rows rows below the first in the tensor map of W. A row tile may start at
+// any row; the rows it holds past its run are multiplied with the wrong matrix and never stored. tiles == nullptr: a
+// plain product. The list is written by a kernel in front, so a grouped product asks for nothing before its wait.
+struct T5Groups {
+  const int* tiles;
+  const int* n_tiles;
+  int w_rows;
+};
+
 template <int T5_BN, class P>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ y, int ldy, int M, int N, int K, int mode, float out_scale, int gate_rows,
-                    int tiles_n, int num_tiles, int group_m, int* __restrict__ status, const QkvRope rope) {
+                    int tiles_n, int num_tiles_plain, int group_m, int* __restrict__ status, const QkvRope rope,
+                    const T5Groups groups) {
   constexpr int T5_STAGES = T5<T5_BN>::STAGES;
   constexpr uint32_t T5_B_BYTES = T5<T5_BN>::B_BYTES, T5_STAGE_BYTES = T5<T5_BN>::STAGE_BYTES, T5_TMEM_COLS = T5<T5_BN>::TMEM_COLS;
   extern __shared__ unsigned char t5_raw[];
@@ -84,6 +96,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const bool swiglu = mode == T5_OUT_SWIGLU;
   const int n_per_tile = swiglu ? T5_BN / 2 : T5_BN;      // output features per tile
   const int k_tiles = (K + T5_BK - 1) / T5_BK;
+  const bool grouped = groups.tiles != nullptr;
+  // (first row, first feature, first row of W's matrix, one past the last row to store) of a tile
+  auto coords = [&](int tile, int num_tiles, int* m0, int* n0, int* w0, int* m_end) {
+    if (grouped) {
+      const int* g = groups.tiles + 3 * (tile / tiles_n);
+      *m0 = g[1];
+      *m_end = g[1] + g[2];
+      *n0 = (tile % tiles_n) * n_per_tile;
+      *w0 = g[0] * groups.w_rows;
+    } else {
+      int m_tile, n_tile;
+      t5_tile_coords(tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
+      *m0 = (m_tile * P::CLUSTER + rank) * T5_BM;
+      *n0 = n_tile * n_per_tile;
+      *w0 = 0;
+      *m_end = M;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T5_STAGES; ++s) {
@@ -125,11 +155,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     auto load_x = [&](int s, int kt, int m0) {
       tma_load_2d(tiles + static_cast<size_t>(s) * T5_STAGE_BYTES, &map_x, kt * T5_BK, m0, &full_bar[s]);
     };
-    const int ahead = first_tile < num_tiles ? min(k_tiles, T5_STAGES) : 0;
+    const int ahead = (!grouped && first_tile < num_tiles_plain) ? min(k_tiles, T5_STAGES) : 0;
     if (ahead > 0) {
-      int m_tile, n_tile;
-      t5_tile_coords(first_tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
-      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
+      int m0, n0, w0, m_end;
+      coords(first_tile, num_tiles_plain, &m0, &n0, &w0, &m_end);
       if (elect_one()) {
         for (int kt = 0; kt < ahead; ++kt) {
           mbar_expect_tx(&full_bar[kt], T5_STAGE_BYTES);
@@ -147,12 +176,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       pdl_wait();
       pdl_trigger();
     }
+    const int num_tiles = grouped ? groups.n_tiles[0] * tiles_n : num_tiles_plain;      // (after the wait)
     uint32_t it = ahead;                           // k-slices issued so far, over all tiles
     bool ok = true;
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-      int m_tile, n_tile;
-      t5_tile_coords(tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
-      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
+      int m0, n0, w0, m_end;
+      coords(tile, num_tiles, &m0, &n0, &w0, &m_end);
+      n0 += w0;                                    // the row of W's tensor map
       for (int kt = tile == first_tile ? ahead : 0; kt < k_tiles; ++kt, ++it) {
         const int s = it % T5_STAGES;
         if (it >= T5_STAGES && !warp_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
@@ -173,6 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // MMA issue: the whole warp runs the loop, one elected lane issues the instructions
     constexpr uint32_t idesc = umma_idesc(T5_BM, T5_BN);
     const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));      // a step along the tiles adds (bytes >> 4)
+    const int num_tiles = grouped ? groups.n_tiles[0] * tiles_n : num_tiles_plain;
     uint32_t it = 0, local = 0;                    // k-slices consumed; tiles done by this block
     bool ok = true;
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
@@ -208,12 +239,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     pdl_trigger();
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
+    const int num_tiles = grouped ? groups.n_tiles[0] * tiles_n : num_tiles_plain;
+    const int M_all = M;
     uint32_t local = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
       const uint32_t buf = local & 1;
-      int m_tile, n_tile;
-      t5_tile_coords(tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
-      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
+      int m0, n0, w0, M;                           // M: one past the last row this tile may store
+      coords(tile, num_tiles, &m0, &n0, &w0, &M);
+      M = min(M, M_all);
       const int row = m0 + quarter * 32 + lane;
       if (!warp_wait(&acc_full[buf], (local >> 1) & 1, status, T5_ERR_EPILOGUE, abort_flag)) break;
       tcgen05_after_sync();
@@ -488,7 +521,7 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<256>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<256, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope, dl::T5Groups{nullptr, nullptr, 0}));
   } else if (bn == 192) {
     static bool configured = false;
     if (!configured) {
@@ -499,7 +532,7 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<192>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<192, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope, dl::T5Groups{nullptr, nullptr, 0}));
   } else {
     static bool configured = false;
     if (!configured) {
@@ -510,8 +543,68 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<128>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<128, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope, dl::T5Groups{nullptr, nullptr, 0}));
   }
+}
+
+// A grouped product (see T5Groups): a bf16 [rows, K] whose runs of rows are listed in `tiles`, w bf16 [matrices, N, K]
+// contiguous, y [rows, N] bf16 (mode 0, or 4 with the squared ReLU) or fp32 (mode 1). max_row_tiles: the most row tiles
+// the list can hold; the grid is sized for it and blocks past the list's end do nothing.
+template <class P>
+static int t5_launch_grouped(const void* a, int lda, int rows, const void* w, int matrices, int N, int K, void* y, int ldy,
+                             int mode, const int* tiles, const int* n_tiles, int max_row_tiles, int* status,
+                             cudaStream_t stream) {
+  static_assert(P::CLUSTER == 1, "a grouped product runs every block for itself");
+  if (rows <= 0 || N <= 0 || max_row_tiles <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(y) & 15) || status == nullptr || tiles == nullptr || n_tiles == nullptr || matrices <= 0 ||
+      (mode != dl::T5_OUT_BF16 && mode != dl::T5_OUT_F32 && mode != dl::T5_OUT_RELU2) ||
+      (mode == dl::T5_OUT_F32 ? (N & 3) || (ldy & 3) : (N & 7) || (ldy & 7)) ||
+      static_cast<long long>(matrices) * N > (1ll << 30))
+    return DL_ERR_UNSUPPORTED;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const int bn = N >= 256 ? 256 : 128;
+  const int tiles_n = (N + bn - 1) / bn;
+  const long long most = static_cast<long long>(max_row_tiles) * tiles_n;
+  if (most > (1ll << 30)) return DL_ERR_UNSUPPORTED;
+  CUtensorMap map_x, map_w;
+  int rc = dl::make_map(&map_x, a, rows, K, lda, dl::T5_BM);
+  if (rc != 0) return rc;
+  rc = dl::make_map(&map_w, w, matrices * N, K, K, bn / 2);
+  if (rc != 0) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(most < sm_count ? most : sm_count));
+  cfg.blockDim = dim3(dl::T5_THREADS);
+  cfg.stream = stream;
+  const dl::QkvRope none = {};
+  const dl::T5Groups groups = {tiles, n_tiles, N};
+  if (bn == 256) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel<256, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(dl::T5<256>::SMEM));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    cfg.dynamicSmemBytes = dl::T5<256>::SMEM;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<256, P>, map_x, map_w, y, ldy, rows, N, K, mode,
+                                               1.0f, 0, tiles_n, 0, 1, status, none, groups));
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel<128, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dl::T5<128>::SMEM));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cfg.dynamicSmemBytes = dl::T5<128>::SMEM;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<128, P>, map_x, map_w, y, ldy, rows, N, K, mode,
+                                             1.0f, 0, tiles_n, 0, 1, status, none, groups));
 }
 
 // Fills the epilogue's parameters for the q | k | v product and launches it (see dl_gemm_tcgen05_qkv_rope).

@@ -284,6 +284,16 @@ moe_linear_tc_kernel(const bf16* __restrict__ a, int lda, const int* __restrict_
       }
 }
 
+// out[place] = a[pair_at[place] / top_div]: the rows of a step in the order of their experts, 16 bytes a thread.
+__global__ void moe_gather_kernel(const uint4* __restrict__ a, int lda16, const int* __restrict__ pair_at, int top_div,
+                                  uint4* __restrict__ out, int row16, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t place = i / row16;
+  const int c = static_cast<int>(i % row16);
+  out[i] = a[static_cast<size_t>(pair_at[place] / top_div) * lda16 + c];
+}
+
 template <typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ c, int width, const int* __restrict__ place_of,
                                    const float* __restrict__ weights, int top, TO* __restrict__ y, size_t total) {
@@ -370,6 +380,18 @@ DL_EXPORT int dl_moe_linear(int dtype, int out_dtype, const void* a, int lda, co
   else if (dtype == 1 && out_dtype == 0) DL_MOE(dl::bf16, float);
   else return DL_ERR_UNSUPPORTED;
 #undef DL_MOE
+  return dl::launch_status();
+}
+
+// out [pairs, K] = the rows of a (bf16, K a multiple of 8, lda a multiple of 8, both 16-byte aligned) in place order.
+DL_EXPORT int dl_moe_gather(const void* a, int lda, const int* pair_at, int top_div, void* out, int pairs, int K,
+                            cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || top_div <= 0 || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return DL_ERR_UNSUPPORTED;
+  const size_t total = static_cast<size_t>(pairs) * (K / 8);
+  dl::moe_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(a), lda / 8, pair_at, top_div, static_cast<uint4*>(out), K / 8, total);
   return dl::launch_status();
 }
 

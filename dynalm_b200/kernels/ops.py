@@ -94,6 +94,7 @@ _SIGNATURES = {
         "dl_moe_route": [_P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P],
         "dl_moe_group": [_P, _I, _I, _P, _P, _P, _P, _I, _P],
         "dl_moe_linear": [_I, _I, _P, _I, _P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+        "dl_moe_gather": [_P, _I, _P, _I, _P, _I, _I, _P],
         "dl_moe_combine": [_I, _P, _I, _P, _P, _I, _P, _I, _P]},
     "gates": {
         "dl_gelu_mul": [_I, _P, _P, _I, _I, _P],
@@ -119,6 +120,7 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
         "dl_gemm_tcgen05_tile_coords": [_I, _I, _I, _I, _P, _P],
+        "dl_gemm_tcgen05_grouped": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _I, _P, _P, _I, _P, _P],
         "dl_gemm_tcgen05_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
     "gemm_tcgen05_cluster": {
         "dl_gemm_tcgen05_cluster": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -2101,3 +2103,42 @@ def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v
         _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table), block_table.stride(0), _p(q_tiles),
         n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, key_dim, value_dim, page_size, scale, window, int(keep_first),
         1 if sink else 0, _stream()), "masked_flash_attention")
+
+
+MOE_TCGEN05 = os.environ.get("DYNALM_MOE_TCGEN05", "1") != "0"      # 0: the experts' products of long steps on mma.sync
+
+
+def moe_gather(a: torch.Tensor, pair_at: torch.Tensor, top_div: int, out: torch.Tensor) -> None:
+    """out[place] = a[pair_at[place] // top_div]: the rows of a step (bfloat16) in the order of their experts."""
+    _cuda(a, pair_at, out)
+    _rows_contiguous(a, "a")
+    pairs, K = out.shape
+    if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not out.is_contiguous() or a.shape[1] != K \
+            or pair_at.dtype != torch.int32 or pair_at.numel() < pairs:
+        raise InvalidArgument("moe_gather: a [rows, K] and out [pairs, K] bfloat16, pair_at int32 [pairs]")
+    _check(_fn("moe", "dl_moe_gather")(_p(a), a.stride(0), _p(pair_at), top_div, _p(out), pairs, K, _stream()), "moe_gather")
+
+
+def moe_linear_tcgen05_applies(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
+    """Whether the grouped tcgen05 product takes these operands (bfloat16, aligned rows, an output it can store)."""
+    n = w.shape[1]
+    return (MOE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and a.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and c.data_ptr() % 16 == 0 and c.stride(1) == 1
+            and (n % 8 == 0 and c.stride(0) % 8 == 0 if c.dtype == torch.bfloat16 else n % 4 == 0 and c.stride(0) % 4 == 0))
+
+
+def moe_linear_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor,
+                       max_tiles: int, act: str = "none") -> None:
+    """c[place] = act(a[place] w[expert of place]^T) on the tcgen05 tensor cores: a [places, K] bfloat16 IN PLACE ORDER
+    (moe_gather), w [experts, N, K], c [places, N] bfloat16 or float32 (act "none" only), tiles of at most 128 places as
+    moe_group lists them with tile_rows = 128. See csrc/gemm_tcgen05.cu (dl_gemm_tcgen05_grouped)."""
+    _cuda(a, w, c, tiles, n_tiles)
+    if not moe_linear_tcgen05_applies(a, w, c) or w.dim() != 3 or a.shape[1] != w.shape[2] or c.shape != (a.shape[0], w.shape[1]) \
+            or act not in ("none", "relu2") or (act == "relu2" and c.dtype != torch.bfloat16):
+        raise Unsupported("moe_linear_tcgen05: bfloat16 operands with 16-byte aligned rows; relu2 with a bfloat16 result")
+    mode = 4 if act == "relu2" else (0 if c.dtype == torch.bfloat16 else 1)
+    status = _status_word(a.device)
+    _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05_grouped")(
+        _p(a), a.stride(0), a.shape[0], _p(w), w.shape[0], w.shape[1], w.shape[2], _p(c), c.stride(0), mode, _p(tiles),
+        _p(n_tiles), max_tiles, _p(status), _stream()), "moe_linear_tcgen05")

@@ -76,9 +76,17 @@ class RoutedMLP:
         ops.moe_group(ids, pairs, E, place_of, pair_at, tiles, n_tiles, tile_rows)
         max_tiles = ops.moe_max_tiles(pairs, E, tile_rows)
         act = rt.flat(f"moe_act_{top}_{s.inner}", most * s.inner, x.dtype)[:pairs * s.inner].view(pairs, s.inner)
-        ops.moe_linear(x, pair_at, top, self.w_up, act, tiles, n_tiles, max_tiles, "relu2", tile_rows)
         per_pair = rt.flat(f"moe_out_{top}_{s.width}", most * s.width, torch.float32)[:pairs * s.width].view(pairs, s.width)
-        ops.moe_linear(act, None, 1, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none", tile_rows)
+        if tile_rows == ops.MOE_WIDE_TILE_ROWS and ops.moe_linear_tcgen05_applies(x, self.w_up, act) \
+                and ops.moe_linear_tcgen05_applies(act, self.w_down, per_pair):
+            # a long step: the rows once in the order of their experts, then both products on the tcgen05 tensor cores
+            sorted_rows = rt.flat(f"moe_rows_{top}_{s.width}", most * s.width, x.dtype)[:pairs * s.width].view(pairs, s.width)
+            ops.moe_gather(x, pair_at, top, sorted_rows)
+            ops.moe_linear_tcgen05(sorted_rows, self.w_up, act, tiles, n_tiles, max_tiles, "relu2")
+            ops.moe_linear_tcgen05(act, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none")
+        else:
+            ops.moe_linear(x, pair_at, top, self.w_up, act, tiles, n_tiles, max_tiles, "relu2", tile_rows)
+            ops.moe_linear(act, None, 1, self.w_down, per_pair, tiles, n_tiles, max_tiles, "none", tile_rows)
         y = rt.buffer("ffn_out", (rows, s.width))
         ops.moe_combine(per_pair, place_of, weights, top, y)
         return y

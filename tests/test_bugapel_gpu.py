@@ -420,7 +420,7 @@ def test_router_picks_experts_of_the_best_groups(E, top, groups, keep):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("E,top,width,inner,rows", [(6, 2, 96, 40, 50), (4, 1, 64, 32, 7), (5, 5, 72, 17, 33), (8, 4, 256, 128, 300),
-                                                    (3, 2, 128, 64, 1), (16, 2, 160, 224, 130)])
+                                                    (3, 2, 128, 64, 1), (16, 2, 160, 224, 130), (4, 2, 192, 320, 700)])
 def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
     """The whole feed-forward after the router: pairs grouped by expert (some experts get none, one gets more than a
     tile), both products with the squared ReLU between them, the weighted sum in the order of a token's experts."""
@@ -464,6 +464,19 @@ def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
         y = torch.zeros(rows, width, dtype=dtype, device=DEV)
         ops.moe_combine(out, place_of, _t(weights), top, y)
         _close(_np(y), want, 3e-5 if dtype == torch.float32 else 3e-2, f"the experts' weighted sum, tiles of {tile_rows}")
+        if tile_rows == ops.MOE_WIDE_TILE_ROWS and ops.moe_linear_tcgen05_applies(_t(x, dtype), _t(up, dtype), act):
+            # the same on the tcgen05 tensor cores, from rows gathered into the order of their experts
+            rows_sorted = torch.zeros(pairs, width, dtype=dtype, device=DEV)
+            ops.moe_gather(_t(x, dtype), pair_at, top, rows_sorted)
+            assert torch.equal(rows_sorted, _t(x, dtype)[(pair_at // top).long()])
+            act2 = torch.zeros(pairs, inner, dtype=dtype, device=DEV)
+            ops.moe_linear_tcgen05(rows_sorted, _t(up, dtype), act2, tiles, n_tiles, max_tiles, "relu2")
+            out2 = torch.zeros(pairs, width, device=DEV)
+            ops.moe_linear_tcgen05(act2, _t(down, dtype), out2, tiles, n_tiles, max_tiles, "none")
+            assert ops.gemm_tcgen05_status() == 0
+            y2 = torch.zeros(rows, width, dtype=dtype, device=DEV)
+            ops.moe_combine(out2, place_of, _t(weights), top, y2)
+            _close(_np(y2), want, 3e-2, "the experts' weighted sum on tcgen05")
 
 
 # ---------------------------------------------------------------------------------------------
