@@ -122,6 +122,7 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
     }
     if ((tid & ~31) / P < cols) {                 // warps that hold columns; all their lanes walk the tile (the shuffles
       const int clr = cl < cols ? cl : cols - 1;  // name the whole warp), the other warps of the block only fetch
+#pragma unroll 4
       for (int t = 0; t < nt; ++t) {
         const float v = s_v[t * cols + clr];
         const float* qa = s_q + t * Dp;
@@ -144,7 +145,9 @@ gla_scan_kernel(const T* __restrict__ proj, int stride, int q_col, int k_col, in
           acc = fmaf(s[2], q4.z, acc);
           acc = fmaf(s[3], q4.w, acc);
         }
-        for (int off = P >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+          if (off < P) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (p == 0 && cl < cols) s_o[t * cols + cl] = acc;
       }
     }
@@ -197,9 +200,9 @@ DL_EXPORT int dl_gla_scan(int dtype, const void* proj, int stride, int q_col, in
   int P = 1;
   while (P * 16 < d) P <<= 1;                      // lanes a column: the fewest that leave a lane at most 16 rows
   // A warp walks its tokens one after the other, each a short chain of dependent instructions, so what fills an SM is the
-  // number of warps: while the step has fewer than eight computing warps an SM (one long prompt), a column is laid over
+  // number of warps: while the step has fewer than four computing warps an SM (one long prompt), a column is laid over
   // more lanes (down to four rows a lane), which costs a shuffle a doubling.
-  while (P < 32 && d >= 8 * P && static_cast<long long>(requests) * H * e * P / 32 < 8ll * sm_count) P <<= 1;
+  while (P < 32 && d >= 8 * P && static_cast<long long>(requests) * H * e * P / 32 < 4ll * sm_count) P <<= 1;
   const int R = ((d + P - 1) / P + 3) / 4 * 4;     // rows a lane, in fours
   int cols = 256 / P;                              // columns a block of 256 threads takes
   if (cols > e) cols = e;
