@@ -10,7 +10,9 @@
 //   * a row at position p sees key j <= p if p - j < window (window 0: all) or j < keep_first: the key tiles that hold
 //     kept tokens are walked first, then the tiles of the window;
 //   * with `sink` the denominator of a row's softmax holds one more term exp(0), which carries no value;
-//   * warps whose 16 rows lie past the end of the tile (a one-row tile leaves three of four) skip the arithmetic.
+//   * warps whose 16 rows lie past the end of the tile (a one-row tile leaves three of four) skip the arithmetic;
+//   * in a step whose tiles are all single tokens the rows of a tile are the query heads that share a KV head, so the
+//     keys and values of a token are read once for the group.
 //
 // Key tiles begin at multiples of 64 in absolute position, so the arithmetic of a row does not depend on where its
 // portion was cut nor on its place inside a query tile.
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(MF_THREADS)
 masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, size_t k_row,
                     const bf16* __restrict__ v_cache, size_t v_row, const int* __restrict__ block_table, int max_blocks,
                     const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads, int n_kv_heads,
-                    int page_shift, float scale_log2, int window, int keep_first, int sink) {
+                    int page_shift, float scale_log2, int window, int keep_first, int sink, int grp) {
   constexpr int SUB = MF_TILE / MF_BM;    // blocks per query tile
   constexpr int LDK = KD + 8;             // row strides in elements: 16 bytes of padding keep ldmatrix conflict-free
   constexpr int LDV = VD + 8;
@@ -75,17 +77,21 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 
   const int4 tile = ck_tile(tiles[blockIdx.x / SUB]);
   const int sub = blockIdx.x % SUB;
-  const int req = tile.x, row0 = tile.y + sub * MF_BM, nrows = min(MF_BM, tile.z - sub * MF_BM), pos0 = tile.w + sub * MF_BM;
+  const int req = tile.x, row0 = tile.y + sub * MF_BM, pos0 = tile.w + sub * MF_BM;
+  int nrows = min(MF_BM, tile.z - sub * MF_BM);
   if (nrows <= 0) return;
-  const int head = blockIdx.y;
-  const int kvh = head / (n_heads / n_kv_heads);
+  // grp > 0 (every tile one token): the block takes KV head blockIdx.y, and the rows of its tile are the grp query heads
+  // of that KV head, all at the token's position, so the keys and values are read once for the group
+  const int head = grp > 0 ? static_cast<int>(blockIdx.y) * grp : static_cast<int>(blockIdx.y);      // (the first head of the group)
+  const int kvh = grp > 0 ? static_cast<int>(blockIdx.y) : head / (n_heads / n_kv_heads);
+  if (grp > 0) nrows = grp;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int page_mask = (1 << page_shift) - 1;
   const int* table = block_table + static_cast<size_t>(req) * max_blocks;
   const bool warp_live = warp * 16 < nrows;
 
-  const int pos_last = pos0 + nrows - 1;
+  const int pos_last = grp > 0 ? pos0 : pos0 + nrows - 1;
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;     // the first key of the window any row of the tile reads
   const int j_begin = lo_tile / MF_BN, j_end = pos_last / MF_BN;
   // key tiles in front of the window's that hold kept tokens: 0 .. n_kept - 1
@@ -97,7 +103,8 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   for (int c = tid; c < MF_BM * CHK; c += MF_THREADS) {
     const int r = c / CHK, ch = c % CHK;
     const bool ok = r < nrows;
-    const bf16* src = q + static_cast<size_t>(row0 + (ok ? r : 0)) * q_stride + static_cast<size_t>(head) * KD + ch * 8;
+    const bf16* src = grp > 0 ? q + static_cast<size_t>(row0) * q_stride + static_cast<size_t>(head + (ok ? r : 0)) * KD + ch * 8
+                              : q + static_cast<size_t>(row0 + (ok ? r : 0)) * q_stride + static_cast<size_t>(head) * KD + ch * 8;
     mf_cp_async16(Qs + r * LDK + ch * 8, src, ok);
   }
   auto load_kv = [&](int j, int stage) {
@@ -125,7 +132,7 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   for (int h = 0; h < 2; ++h) {
     m_run[h] = -INFINITY;
     l_run[h] = 0.0f;
-    pos_r[h] = pos0 + warp * 16 + g + h * 8;
+    pos_r[h] = grp > 0 ? pos0 : pos0 + warp * 16 + g + h * 8;
     lo_r[h] = window > 0 ? max(0, pos_r[h] - window + 1) : 0;
   }
   uint32_t qf[KS][4];
@@ -167,7 +174,8 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
       // scale, mask by position, online softmax; P as bf16 A fragments
       const int key0 = j * MF_BN;
       uint32_t pf[MF_BN / 16][4];
-      const bool edge = it < n_kept || key0 + MF_BN - 1 > pos0 + warp * 16 || (window > 0 && key0 < max(lo_r[0], lo_r[1]));
+      const bool edge = it < n_kept || key0 + MF_BN - 1 > (grp > 0 ? pos0 : pos0 + warp * 16) ||
+                        (window > 0 && key0 < max(lo_r[0], lo_r[1]));
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < MF_BN / 8; ++i) {
@@ -249,10 +257,11 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 #pragma unroll
   for (int i = 0; i < VD / 8; ++i) {
     const int col = head * VD + i * 8 + 2 * t;
-    if (r_a < nrows)
-      *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_a) * out_stride + col) = mf_pack(o[i][0] * inv[0], o[i][1] * inv[0]);
-    if (r_b < nrows)
-      *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_b) * out_stride + col) = mf_pack(o[i][2] * inv[1], o[i][3] * inv[1]);
+    // row r of a tile is row row0 + r of the step, or (grp > 0) head `head + r` of row row0
+    bf16* dst_a = grp > 0 ? out + static_cast<size_t>(row0) * out_stride + col + r_a * VD : out + static_cast<size_t>(row0 + r_a) * out_stride + col;
+    bf16* dst_b = grp > 0 ? out + static_cast<size_t>(row0) * out_stride + col + r_b * VD : out + static_cast<size_t>(row0 + r_b) * out_stride + col;
+    if (r_a < nrows) *reinterpret_cast<uint32_t*>(dst_a) = mf_pack(o[i][0] * inv[0], o[i][1] * inv[0]);
+    if (r_b < nrows) *reinterpret_cast<uint32_t*>(dst_b) = mf_pack(o[i][2] * inv[1], o[i][3] * inv[1]);
   }
 }
 
@@ -260,7 +269,7 @@ template <int KD, int VD>
 int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k_row, const void* vc, long long v_row,
                         const int* block_table, int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride,
                         int n_heads, int n_kv_heads, int page_shift, float scale, int window, int keep_first, int sink,
-                        cudaStream_t stream) {
+                        int grp, cudaStream_t stream) {
   constexpr size_t smem = (static_cast<size_t>(MF_BM + 2 * MF_BN) * (KD + 8) + static_cast<size_t>(2 * MF_BN) * (VD + 8)) * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -269,12 +278,12 @@ int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(n_tiles * (MF_TILE / MF_BM), n_heads);
+  dim3 grid(n_tiles * (MF_TILE / MF_BM), grp > 0 ? n_kv_heads : n_heads);
   masked_flash_kernel<KD, VD><<<grid, MF_THREADS, smem, stream>>>(
       static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<size_t>(k_row),
       static_cast<const bf16*>(vc), static_cast<size_t>(v_row), block_table, max_blocks, reinterpret_cast<const int4*>(tiles),
       static_cast<bf16*>(out), out_stride, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, keep_first,
-      sink);
+      sink, grp);
   return launch_status();
 }
 
@@ -287,7 +296,8 @@ int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k
 DL_EXPORT int dl_masked_flash_attention(const void* q, int q_stride, const void* k_cache, long long k_row, const void* v_cache,
                                         long long v_row, const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                         void* out, int out_stride, int n_heads, int n_kv_heads, int key_dim, int value_dim,
-                                        int page_size, float scale, int window, int keep_first, int sink, cudaStream_t stream) {
+                                        int page_size, float scale, int window, int keep_first, int sink, int one_token_tiles,
+                                        cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -295,11 +305,14 @@ DL_EXPORT int dl_masked_flash_attention(const void* q, int q_stride, const void*
       (out_stride & 1) || !(scale > 0.0f) || (k_row & 7) || (v_row & 7) || window < 0 || keep_first < 0 ||
       (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return DL_ERR_UNSUPPORTED;
+  // every tile one token (the caller says so) and heads that share keys: the heads of a KV head are the rows of a tile
+  const int group = n_heads / n_kv_heads;
+  const int grp = (one_token_tiles && group > 1 && group <= dl::MF_BM) ? group : 0;
 #define DL_CASE(K, V)                                                                                                   \
   if (key_dim == K && value_dim == V)                                                                                   \
     return dl::launch_masked_flash<K, V>(q, q_stride, k_cache, k_row, v_cache, v_row, block_table, max_blocks, tiles,   \
                                          n_tiles, out, out_stride, n_heads, n_kv_heads, page_shift, scale, window,      \
-                                         keep_first, sink, stream)
+                                         keep_first, sink, grp, stream)
   DL_CASE(16, 16); DL_CASE(32, 32); DL_CASE(48, 48); DL_CASE(64, 64); DL_CASE(80, 80); DL_CASE(96, 96); DL_CASE(112, 112);
   DL_CASE(128, 128);
   DL_CASE(32, 16); DL_CASE(48, 32); DL_CASE(64, 32); DL_CASE(96, 48); DL_CASE(96, 64); DL_CASE(128, 64); DL_CASE(64, 128);

@@ -83,7 +83,7 @@ _SIGNATURES = {
         "dl_qk_rot_head_norm_cache": [_I, _P, _I, _P, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I,
                                       _P]},
     "attention_masked_flash": {
-        "dl_masked_flash_attention": [_P, _I, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P]},
+        "dl_masked_flash_attention": [_P, _I, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P]},
     "layer_norm": {
         "dl_stream_layer_norm": [_I, _I, _P, _I, _I, _P, _P, _I, _L, _F, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
         "dl_stream_sum": [_I, _P, _I, _I, _P, _I, _L, _F, _P, _P, _P, _I, _P]},
@@ -2080,11 +2080,12 @@ MASKED_FLASH_SIZES = {(d, d) for d in range(16, 129, 16)} | {(32, 16), (48, 32),
 def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int,
                            block_table: torch.Tensor, q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int,
                            n_kv_heads: int, key_dim: int, value_dim: int, page_size: int, scale: float, window: int = 0,
-                           keep_first: int = 0, sink: bool = False) -> None:
+                           keep_first: int = 0, sink: bool = False, one_token_tiles: bool = False) -> None:
     """Flash attention of query tiles over the paged cache, bfloat16, with keys of key_dim and values of value_dim
     numbers (a pair of MASKED_FLASH_SIZES), kept first tokens behind the window and an optional extra term exp(0) in the
     denominator; see csrc/attention_masked_flash.cu. q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128,
-    first position). k_cache / v_cache point at the first token's keys / values, k_row / v_row elements between tokens."""
+    first position). k_cache / v_cache point at the first token's keys / values, k_row / v_row elements between tokens.
+    one_token_tiles: every tile is a single token (a decode step); the heads that share a KV head then share a block."""
     _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -2102,7 +2103,7 @@ def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v
     _check(_fn("attention_masked_flash", "dl_masked_flash_attention")(
         _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table), block_table.stride(0), _p(q_tiles),
         n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, key_dim, value_dim, page_size, scale, window, int(keep_first),
-        1 if sink else 0, _stream()), "masked_flash_attention")
+        1 if sink else 0, 1 if one_token_tiles else 0, _stream()), "masked_flash_attention")
 
 
 MOE_TCGEN05 = os.environ.get("DYNALM_MOE_TCGEN05", "1") != "0"      # 0: the experts' products of long steps on mma.sync

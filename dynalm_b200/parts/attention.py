@@ -333,7 +333,8 @@ class GatedNormedAttention(PagedAttention):
             k_cache, k_row, v_cache, v_row = self._kv(cache)
             ops.masked_flash_attention(qkv, k_cache, k_row, v_cache, v_row, cache.block_table, q_tiles, n_tiles, out,
                                        s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
-                                       float(s.scale), self.window, self.keep_first, self.sink)
+                                       float(s.scale), self.window, self.keep_first, self.sink,
+                                       one_token_tiles=ctx.decode_only)
             return
         if self.same and self.plain_mask:
             from ..kernels import attention as fast
