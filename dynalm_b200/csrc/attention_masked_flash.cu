@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(MF_THREADS)
 masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, size_t k_row,
                     const bf16* __restrict__ v_cache, size_t v_row, const int* __restrict__ block_table, int max_blocks,
                     const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads, int n_kv_heads,
-                    int page_shift, float scale_log2, int window, int keep_first, int sink, int grp) {
+                    int page_shift, float scale_log2, int window, int keep_first, int sink, int grp, float* __restrict__ partial) {
   constexpr int SUB = MF_TILE / MF_BM;    // blocks per query tile
   constexpr int LDK = KD + 8;             // row strides in elements: 16 bytes of padding keep ldmatrix conflict-free
   constexpr int LDV = VD + 8;
@@ -99,6 +99,11 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   const int n_kept = kept > 0 ? min((kept - 1) / MF_BN + 1, j_begin) : 0;
   const int n_iter = n_kept + (j_end - j_begin + 1);
   auto tile_of = [&](int it) { return it < n_kept ? it : j_begin + (it - n_kept); };
+  // gridDim.z > 1 (single-token tiles of a step with few rows): the key tiles of a row are dealt over that many blocks,
+  // each leaving its maximum, sum and unnormalised output in `partial` for masked_flash_merge_kernel
+  const int n_parts = static_cast<int>(gridDim.z), part = static_cast<int>(blockIdx.z);
+  const int per_part = (n_iter + n_parts - 1) / n_parts;
+  const int it_begin = min(part * per_part, n_iter), it_end = min(it_begin + per_part, n_iter);
 
   for (int c = tid; c < MF_BM * CHK; c += MF_THREADS) {
     const int r = c / CHK, ch = c % CHK;
@@ -120,7 +125,7 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
       else mf_cp_async16(vs + r * LDV + (ch - CHK) * 8, v_cache + slot * v_row + static_cast<size_t>(kvh) * VD + (ch - CHK) * 8, ok);
     }
   };
-  load_kv(tile_of(0), 0);
+  if (it_begin < it_end) load_kv(tile_of(it_begin), 0);
   mf_commit();
 
   float o[VD / 8][4];
@@ -137,15 +142,15 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   }
   uint32_t qf[KS][4];
 
-  for (int it = 0; it < n_iter; ++it) {
+  for (int it = it_begin; it < it_end; ++it) {
     const int j = tile_of(it);
-    const int stage = it & 1;
-    if (it + 1 < n_iter) load_kv(tile_of(it + 1), stage ^ 1);
+    const int stage = (it - it_begin) & 1;
+    if (it + 1 < it_end) load_kv(tile_of(it + 1), stage ^ 1);
     mf_commit();
     mf_wait<1>();
     __syncthreads();
     if (warp_live) {
-      if (it == 0) {
+      if (it == it_begin) {
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
           const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -243,6 +248,26 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   if (!warp_live) return;
 
   const int r_a = warp * 16 + g, r_b = r_a + 8;
+  if (partial != nullptr) {
+    // records [row][head][part] of (maximum in base-2 units, sum, VD unnormalised outputs); a tile here is one token
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = h == 0 ? r_a : r_b;
+      if (r >= nrows) continue;
+      const int head_abs = grp > 0 ? head + r : head;
+      float* rec = partial + ((static_cast<size_t>(row0) * n_heads + head_abs) * n_parts + part) * (VD + 2);
+      if (t == 0) {
+        rec[0] = m_run[h];
+        rec[1] = l_run[h];
+      }
+#pragma unroll
+      for (int i = 0; i < VD / 8; ++i) {
+        rec[2 + i * 8 + 2 * t] = o[i][2 * h];
+        rec[2 + i * 8 + 2 * t + 1] = o[i][2 * h + 1];
+      }
+    }
+    return;
+  }
   float inv[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -265,11 +290,35 @@ masked_flash_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   }
 }
 
+// out[row][head] = sum_p o_p 2^(m_p - M) / (sum_p l_p 2^(m_p - M) + [sink] 2^(-M)), M = max_p m_p (and 0 with the sink):
+// the parts of a row and head that masked_flash_kernel left, in the order of the parts.
+__global__ void masked_flash_merge_kernel(const float* __restrict__ partial, int n_parts, int VD, int n_heads, int sink,
+                                          bf16* __restrict__ out, int out_stride) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const float* rec = partial + (static_cast<size_t>(row) * n_heads + head) * n_parts * (VD + 2);
+  float M = sink ? 0.0f : -INFINITY;
+  for (int p = 0; p < n_parts; ++p) M = fmaxf(M, rec[p * (VD + 2)]);
+  float l = sink ? mf_exp2(-M) : 0.0f;
+  for (int p = 0; p < n_parts; ++p) {
+    const float m = rec[p * (VD + 2)];
+    if (m != -INFINITY) l += rec[p * (VD + 2) + 1] * mf_exp2(m - M);
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  for (int v = threadIdx.x; v < VD; v += blockDim.x) {
+    float acc = 0.0f;
+    for (int p = 0; p < n_parts; ++p) {
+      const float m = rec[p * (VD + 2)];
+      if (m != -INFINITY) acc = fmaf(rec[p * (VD + 2) + 2 + v], mf_exp2(m - M), acc);
+    }
+    out[static_cast<size_t>(row) * out_stride + head * VD + v] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 template <int KD, int VD>
 int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k_row, const void* vc, long long v_row,
                         const int* block_table, int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride,
                         int n_heads, int n_kv_heads, int page_shift, float scale, int window, int keep_first, int sink,
-                        int grp, cudaStream_t stream) {
+                        int grp, int parts, float* partial, int rows, cudaStream_t stream) {
   constexpr size_t smem = (static_cast<size_t>(MF_BM + 2 * MF_BN) * (KD + 8) + static_cast<size_t>(2 * MF_BN) * (VD + 8)) * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -278,12 +327,17 @@ int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(n_tiles * (MF_TILE / MF_BM), grp > 0 ? n_kv_heads : n_heads);
+  dim3 grid(n_tiles * (MF_TILE / MF_BM), grp > 0 ? n_kv_heads : n_heads, parts > 1 ? parts : 1);
   masked_flash_kernel<KD, VD><<<grid, MF_THREADS, smem, stream>>>(
       static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<size_t>(k_row),
       static_cast<const bf16*>(vc), static_cast<size_t>(v_row), block_table, max_blocks, reinterpret_cast<const int4*>(tiles),
       static_cast<bf16*>(out), out_stride, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, keep_first,
-      sink, grp);
+      sink, grp, parts > 1 ? partial : nullptr);
+  if (parts > 1) {
+    dim3 mgrid(rows, n_heads);
+    masked_flash_merge_kernel<<<mgrid, VD < 64 ? 32 : 64, 0, stream>>>(partial, parts, VD, n_heads, sink, static_cast<bf16*>(out),
+                                                                      out_stride);
+  }
   return launch_status();
 }
 
@@ -292,12 +346,13 @@ int launch_masked_flash(const void* q, int q_stride, const void* kc, long long k
 // bfloat16 only. tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128, first position), 16-byte aligned.
 // q rows have head h at column h * key_dim, out rows at column h * value_dim. k_cache / v_cache point at the first
 // token's keys / values (KV head j at j * key_dim / j * value_dim); k_row / v_row elements lie between two tokens.
-// Sizes it takes: key_dim == value_dim in steps of 16 up to 128, and the pairs listed below; others are refused.
+// one_token_tiles: every tile is a single token, tile i being row i of the step; parts > 1 then deals a row's key tiles
+// over that many blocks and merges them (partial: scratch). Sizes it takes: key_dim == value_dim in steps of 16 up to 128, and the pairs listed below; others are refused.
 DL_EXPORT int dl_masked_flash_attention(const void* q, int q_stride, const void* k_cache, long long k_row, const void* v_cache,
                                         long long v_row, const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                         void* out, int out_stride, int n_heads, int n_kv_heads, int key_dim, int value_dim,
                                         int page_size, float scale, int window, int keep_first, int sink, int one_token_tiles,
-                                        cudaStream_t stream) {
+                                        int parts, float* partial, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -308,11 +363,14 @@ DL_EXPORT int dl_masked_flash_attention(const void* q, int q_stride, const void*
   // every tile one token (the caller says so) and heads that share keys: the heads of a KV head are the rows of a tile
   const int group = n_heads / n_kv_heads;
   const int grp = (one_token_tiles && group > 1 && group <= dl::MF_BM) ? group : 0;
+  // parts > 1: every tile is one token, tile i is row i of the step, and `partial` holds n_tiles * n_heads * parts *
+  // (value_dim + 2) floats
+  if (parts > 1 && (!one_token_tiles || partial == nullptr || parts > 64)) return DL_ERR_UNSUPPORTED;
 #define DL_CASE(K, V)                                                                                                   \
   if (key_dim == K && value_dim == V)                                                                                   \
     return dl::launch_masked_flash<K, V>(q, q_stride, k_cache, k_row, v_cache, v_row, block_table, max_blocks, tiles,   \
                                          n_tiles, out, out_stride, n_heads, n_kv_heads, page_shift, scale, window,      \
-                                         keep_first, sink, grp, stream)
+                                         keep_first, sink, grp, parts, partial, n_tiles, stream)
   DL_CASE(16, 16); DL_CASE(32, 32); DL_CASE(48, 48); DL_CASE(64, 64); DL_CASE(80, 80); DL_CASE(96, 96); DL_CASE(112, 112);
   DL_CASE(128, 128);
   DL_CASE(32, 16); DL_CASE(48, 32); DL_CASE(64, 32); DL_CASE(96, 48); DL_CASE(96, 64); DL_CASE(128, 64); DL_CASE(64, 128);

@@ -83,7 +83,8 @@ _SIGNATURES = {
         "dl_qk_rot_head_norm_cache": [_I, _P, _I, _P, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I,
                                       _P]},
     "attention_masked_flash": {
-        "dl_masked_flash_attention": [_P, _I, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P]},
+        "dl_masked_flash_attention": [_P, _I, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _P,
+                                      _P]},
     "layer_norm": {
         "dl_stream_layer_norm": [_I, _I, _P, _I, _I, _P, _P, _I, _L, _F, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
         "dl_stream_sum": [_I, _P, _I, _I, _P, _I, _L, _F, _P, _P, _P, _I, _P]},
@@ -2080,12 +2081,15 @@ MASKED_FLASH_SIZES = {(d, d) for d in range(16, 129, 16)} | {(32, 16), (48, 32),
 def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v_cache: torch.Tensor, v_row: int,
                            block_table: torch.Tensor, q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int,
                            n_kv_heads: int, key_dim: int, value_dim: int, page_size: int, scale: float, window: int = 0,
-                           keep_first: int = 0, sink: bool = False, one_token_tiles: bool = False) -> None:
+                           keep_first: int = 0, sink: bool = False, one_token_tiles: bool = False, parts: int = 1,
+                           partial: Optional[torch.Tensor] = None) -> None:
     """Flash attention of query tiles over the paged cache, bfloat16, with keys of key_dim and values of value_dim
     numbers (a pair of MASKED_FLASH_SIZES), kept first tokens behind the window and an optional extra term exp(0) in the
     denominator; see csrc/attention_masked_flash.cu. q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128,
     first position). k_cache / v_cache point at the first token's keys / values, k_row / v_row elements between tokens.
-    one_token_tiles: every tile is a single token (a decode step); the heads that share a KV head then share a block."""
+    one_token_tiles: every tile is a single token, tile i being row i of q (a decode step); the heads that share a KV head
+    then share a block, and with parts > 1 a row's key tiles are dealt over that many blocks whose results a second
+    kernel merges (partial: float32 scratch of masked_flash_partial_floats elements)."""
     _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -2099,11 +2103,35 @@ def masked_flash_attention(q: torch.Tensor, k_cache: torch.Tensor, k_row: int, v
         raise Unsupported("masked flash attention: q and cache rows must be 16-byte aligned, out rows 4-byte aligned")
     if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
         raise InvalidArgument("masked flash attention: q_tiles must be int32 [n_tiles, 4]")
+    if parts > 1 and (not one_token_tiles or partial is None or partial.dtype != torch.float32
+                      or partial.numel() < masked_flash_partial_floats(n_tiles, n_heads, value_dim, parts) or n_tiles > q.shape[0]):
+        raise InvalidArgument("masked flash attention: parts go with single-token tiles and a float32 scratch for them")
+    _cuda(partial)
     check_limits("attention_masked_flash", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_masked_flash", "dl_masked_flash_attention")(
         _p(q), q.stride(0), _p(k_cache), k_row, _p(v_cache), v_row, _p(block_table), block_table.stride(0), _p(q_tiles),
         n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, key_dim, value_dim, page_size, scale, window, int(keep_first),
-        1 if sink else 0, 1 if one_token_tiles else 0, _stream()), "masked_flash_attention")
+        1 if sink else 0, 1 if one_token_tiles else 0, int(parts), _p(partial) if parts > 1 else None, _stream()),
+        "masked_flash_attention")
+
+
+MASKED_FLASH_MAX_PARTS = 8
+
+
+def masked_flash_partial_floats(rows: int, n_heads: int, value_dim: int, parts: int) -> int:
+    return rows * n_heads * parts * (value_dim + 2)
+
+
+def masked_flash_parts(rows: int, blocks_a_row: int, keys: int) -> int:
+    """Into how many parts a decode step deals a row's key tiles: enough blocks to cover the GPU about twice, a part at
+    least four key tiles (256 keys), at most MASKED_FLASH_MAX_PARTS, a power of two (`keys`: the longest row's, already
+    rounded so that the launch shape changes only now and then)."""
+    from .device import sm_count
+    want = -(-2 * sm_count() // max(1, rows * blocks_a_row))
+    parts = 1
+    while parts * 2 <= min(want, MASKED_FLASH_MAX_PARTS, keys // 256):
+        parts *= 2
+    return parts
 
 
 MOE_TCGEN05 = os.environ.get("DYNALM_MOE_TCGEN05", "1") != "0"      # 0: the experts' products of long steps on mma.sync

@@ -249,7 +249,21 @@ class GatedNormedAttention(PagedAttention):
         return [fast.QUERY_TILES]                  # the masked flash kernel walks the step's query tiles
 
     def graph_key(self, ctx) -> tuple:
-        return super().graph_key(ctx) if self.same and self.plain_mask and self.rt.dtype == torch.bfloat16 else ()
+        if self.same and self.plain_mask:
+            return super().graph_key(ctx) if self.rt.dtype == torch.bfloat16 else ()
+        return (("masked_flash_parts", self._decode_parts(ctx)),) if self.rt.dtype == torch.bfloat16 else ()
+
+    def _decode_parts(self, ctx) -> int:
+        """Into how many parts a step of single tokens deals a row's keys (part of the launch shape, so of the graph key)."""
+        if not ctx.decode_only:
+            return 1
+        s = self.spec
+        span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + self.keep_first)
+        bucket = 256
+        while bucket < span:
+            bucket *= 2
+        group = s.num_heads // s.num_kv_heads
+        return ops.masked_flash_parts(ctx.num_tokens, s.num_kv_heads if 1 < group <= 64 else s.num_heads, bucket)
 
     def cache_spec(self) -> Optional[CacheSpec]:
         s = self.spec
@@ -331,10 +345,16 @@ class GatedNormedAttention(PagedAttention):
             from ..kernels import attention as fast
             q_tiles, n_tiles, _, _ = fast.query_tiles(ctx)
             k_cache, k_row, v_cache, v_row = self._kv(cache)
+            parts = self._decode_parts(ctx)
+            partial = None
+            if parts > 1:
+                most = max(self.rt.max_requests, qkv.shape[0])
+                partial = self.rt.flat(f"masked_flash_parts_{s.num_heads}x{s.value_dim}",
+                                       ops.masked_flash_partial_floats(most, s.num_heads, s.value_dim, ops.MASKED_FLASH_MAX_PARTS))
             ops.masked_flash_attention(qkv, k_cache, k_row, v_cache, v_row, cache.block_table, q_tiles, n_tiles, out,
                                        s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size,
                                        float(s.scale), self.window, self.keep_first, self.sink,
-                                       one_token_tiles=ctx.decode_only)
+                                       one_token_tiles=ctx.decode_only, parts=parts, partial=partial)
             return
         if self.same and self.plain_mask:
             from ..kernels import attention as fast

@@ -231,6 +231,15 @@ def test_attention_with_kept_first_tokens_and_a_sink(dtype, H, G, d, e, window, 
         ops.masked_flash_attention(_t(qs.reshape(len(rows), H * d), dtype), cache, rec, cache.view(-1)[G * d:], rec, table,
                                    tiles, len(rows), grouped, H, G, d, e, page, 1.0, window, keep, sink, one_token_tiles=True)
         _close(_np(grouped), _np(flash), 1e-6, "heads of a group in one block")
+        for parts in (2, 5, 8):                                              # a row's key tiles dealt over blocks, then merged
+            scratch = torch.zeros(ops.masked_flash_partial_floats(len(rows), H, e, parts), device=DEV)
+            dealt = torch.zeros(len(rows), H * e, dtype=dtype, device=DEV)
+            ops.masked_flash_attention(_t(qs.reshape(len(rows), H * d), dtype), cache, rec, cache.view(-1)[G * d:], rec, table,
+                                       tiles, len(rows), dealt, H, G, d, e, page, 1.0, window, keep, sink, one_token_tiles=True,
+                                       parts=parts, partial=scratch)
+            for r, (i, j) in enumerate(zip(rows, targets)):
+                want = plain.attend(qs[r:r + 1], k[:i + 1], v[:i + 1], [i], list(range(i + 1)), 1.0, window, keep, sink)
+                _close(_np(dealt[r]).reshape(1, H, e), want, 2e-2, f"{parts} parts, query {i} pointed at key {j}")
     for r, (i, j) in enumerate(zip(rows, targets)):
         want = plain.attend(qs[r:r + 1], k[:i + 1], v[:i + 1], [i], list(range(i + 1)), 1.0, window, keep, sink)
         _close(_np(out[r]).reshape(1, H, e), want, 2e-5 if dtype == torch.float32 else 2e-2, f"query {i} pointed at key {j}")
