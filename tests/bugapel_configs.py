@@ -71,9 +71,9 @@ B_B = {"architecture": "Bugapel", "vocab": 257, "width": 72, "norm": {"eps": 1e-
 B_C = {"architecture": "Bugapel", "vocab": 512, "width": 128, "norm": {"eps": 1e-5},
        "layers": [
            layer("gla", gla(2, 128, 64, 16.0, 16), moe(64, 4, 2, 1.0, groups=(2, 1))),
-           layer("attention", attention(4, 1, 64, 64, 1.0, dims=32, base=1e6, stretch=(8.0, 1.0, 4.0, 256)),
+           layer("attention", attention(4, 1, 64, 64, 1.0, dims=32, base=2e5, stretch=(6.0, 1.0, 3.0, 256)),
                  moe(64, 4, 2, 1.5)),
-           layer("attention_2", attention_2(2, 2, 128, 128, 0.09, window=160, keep_first=64, dims=128, base=5e5),
+           layer("attention_2", attention_2(2, 2, 128, 128, 0.09, window=160, keep_first=64, dims=128, base=3e5),
                  moe(32, 8, 4, 1.0, groups=(4, 3))),
        ]}
 

@@ -190,7 +190,7 @@ def _attention_case(rng, n, H, G, d, e, dtype, page, shuffle=True):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,e,window,keep,sink", [(4, 2, 32, 16, 20, 3, False), (3, 3, 20, 12, 64, 1, False),
-                                                      (6, 1, 48, 32, 0, 0, True), (2, 1, 40, 8, 700, 5, True),
+                                                      (8, 2, 48, 32, 0, 0, True), (2, 1, 40, 8, 700, 5, True),
                                                       (2, 2, 128, 128, 160, 64, False), (5, 5, 24, 24, 600, 2, True)])
 def test_attention_with_kept_first_tokens_and_a_sink(dtype, H, G, d, e, window, keep, sink):
     """Every query is pointed at one key by a large score: the key just inside the window and the one just outside, the
@@ -247,7 +247,7 @@ def test_attention_with_kept_first_tokens_and_a_sink(dtype, H, G, d, e, window, 
             _close(_np(flash[r]).reshape(1, H, e), want, 2e-2, f"flash kernel, query {i} pointed at key {j}")
 
 
-@pytest.mark.parametrize("H,G,d,e,window,keep,sink", [(4, 2, 32, 16, 20, 3, False), (6, 1, 48, 32, 0, 0, True),
+@pytest.mark.parametrize("H,G,d,e,window,keep,sink", [(4, 2, 32, 16, 20, 3, False), (8, 2, 48, 32, 0, 0, True),
                                                       (2, 2, 128, 128, 160, 64, False), (3, 3, 64, 64, 70, 2, True),
                                                       (2, 1, 96, 48, 64, 65, False), (4, 4, 16, 16, 129, 1, True)])
 def test_masked_flash_attention_on_portions(H, G, d, e, window, keep, sink):
@@ -406,7 +406,7 @@ def test_linear_attention_reads_after_the_write_and_decays_rows():
     _close(_np(o[1]), (5.0 * 0.5 ** (1 / tau) + 1.0) * d ** -0.5 * v, 1e-5, "decay by key channel")
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(6, 2, 3, 2), (8, 4, 2, 1), (5, 5, 1, 1), (8, 2, 4, 2), (1, 1, 1, 1), (12, 3, 3, 3),
+@pytest.mark.parametrize("E,top,groups,keep", [(6, 2, 3, 2), (8, 3, 2, 1), (5, 5, 1, 1), (8, 2, 4, 2), (1, 1, 1, 1), (12, 3, 3, 3),
                                                (64, 6, 8, 3)])
 def test_router_picks_experts_of_the_best_groups(E, top, groups, keep):
     """Random logits, and rows made so that the best expert of all sits in a group that loses: a group's score is its
@@ -432,7 +432,7 @@ def test_router_picks_experts_of_the_best_groups(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,width,inner,rows", [(6, 2, 96, 40, 50), (4, 1, 64, 32, 7), (5, 5, 72, 17, 33), (8, 4, 256, 128, 300),
+@pytest.mark.parametrize("E,top,width,inner,rows", [(6, 2, 96, 40, 50), (4, 1, 64, 32, 7), (5, 5, 72, 17, 33), (8, 3, 256, 128, 300),
                                                     (3, 2, 128, 64, 1), (16, 2, 160, 224, 130), (4, 2, 192, 320, 700)])
 def test_experts_over_grouped_pairs(dtype, E, top, width, inner, rows):
     """The whole feed-forward after the router: pairs grouped by expert (some experts get none, one gets more than a
