@@ -98,11 +98,13 @@ class Block:
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
-    """parts: mixer_norm, mixer, ffn_norm, ffn; parameter: residual_scale (default 1)."""
+    """parts: mixer_norm, mixer, and optionally ffn_norm + ffn; parameter: residual_scale (default 1). Without a
+    feed-forward the layer is x += s * mixer(norm1(x))."""
 
     def __init__(self, spec, store, runtime):
         super().__init__(spec, store, runtime)
         self.scale = float(spec.get("residual_scale", 1.0))
+        self.has_ffn = "ffn" in spec.parts
 
     def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
         rows, width = stream.x.shape
@@ -113,6 +115,10 @@ class PreNormBlock(Block):
             ops.stream_ahead(getattr(self.mixer, "first_weights", lambda: None)())
         self.mixer_norm.forward(stream.x, h, delta=stream.pending, delta_scale=stream.pending_scale)
         a = self.mixer.forward(h, ctx, cache, owns_cache)
+        if not self.has_ffn:
+            stream.pending, stream.pending_scale = a, self.scale
+            stream.as_input = None
+            return stream
         h = self.rt.buffer("normed", (rows, width))
         if few:
             ops.stream_ahead(getattr(self.ffn, "first_weights", lambda: None)())

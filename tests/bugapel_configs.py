@@ -67,7 +67,8 @@ B_B = {"architecture": "Bugapel", "vocab": 257, "width": 72, "norm": {"eps": 1e-
        ]}
 
 # A plain residual stream (no `streams`), no cap, no embedding scale. Heads of 64 and 128 as a served model has them, a
-# window of two pages and a half with a page's worth of kept tokens, a wide linear-attention state.
+# window of two pages and a half with a page's worth of kept tokens, a wide linear-attention state, and a last layer
+# without a feed-forward whose window keeps no first tokens (its pages go back as the window passes).
 B_C = {"architecture": "Bugapel", "vocab": 512, "width": 128, "norm": {"eps": 1e-5},
        "layers": [
            layer("gla", gla(2, 128, 64, 16.0, 16), moe(64, 4, 2, 1.0, groups=(2, 1))),
@@ -75,6 +76,7 @@ B_C = {"architecture": "Bugapel", "vocab": 512, "width": 128, "norm": {"eps": 1e
                  moe(64, 4, 2, 1.5)),
            layer("attention_2", attention_2(2, 2, 128, 128, 0.09, window=160, keep_first=64, dims=128, base=3e5),
                  moe(32, 8, 4, 1.0, groups=(4, 3))),
+           layer("attention_2", attention_2(2, 2, 64, 64, 0.12, window=100, dims=32, base=1e4)),
        ]}
 
 BUGAPEL = {"ba": (B_A, 21), "bb": (B_B, 22), "bc": (B_C, 23)}
